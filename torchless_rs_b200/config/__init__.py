@@ -4,11 +4,12 @@ from .spec import LayerSpec, ModelSpec, PartSpec
 from .mistral import MistralConfig
 from .kikopel import KikopelConfig
 from .tovapel import TovapelConfig
+from .rupasun import RupasunConfig
 from .registry import (architecture_names, config_from_dict, load_config,
                        register_architecture)
 
 __all__ = [
     "ConfigError", "UnknownArchitectureError", "KeyReader", "read_config_json",
-    "LayerSpec", "ModelSpec", "PartSpec", "MistralConfig", "KikopelConfig", "TovapelConfig", "architecture_names",
+    "LayerSpec", "ModelSpec", "PartSpec", "MistralConfig", "KikopelConfig", "TovapelConfig", "RupasunConfig", "architecture_names",
     "config_from_dict", "load_config", "register_architecture",
 ]

@@ -63,6 +63,8 @@ def _register_builtin() -> None:
     register_architecture("Kikopel")(KikopelConfig)
     from .tovapel import TovapelConfig
     register_architecture("Tovapel")(TovapelConfig)
+    from .rupasun import RupasunConfig
+    register_architecture("Rupasun")(RupasunConfig)
 
 
 _register_builtin()

@@ -88,6 +88,94 @@ extern "C" int TL_NAME(tl_moe_route)(const float* z, int ldz, const float* corr,
                    T);
 }
 
+// The choice among grouped experts by sigmoid scores.
+//   s = sigmoid(z) (32-bit).  The n_out experts form `groups` equal groups of neighbours; a group's
+//   score is the sum of its two largest s (of its one, if groups have one member); only experts of
+//   the `keep` best groups can be chosen (ties: the lower group); among them the `top` largest s are
+//   chosen (ties: the lower index); their weights are s / (sum of the chosen s + 1e-20) * scale.
+// A warp per token; scores, group scores and group flags in the warp's shared memory.
+#define MOE_GROUPED_WARPS 4
+#define MOE_GROUPED_MAX 512
+__global__ void __launch_bounds__(MOE_GROUPED_WARPS * 32)
+moe_route_grouped_kernel(const float* __restrict__ z, int ldz, int n_out, int groups, int keep, int top,
+                         float scale, int* __restrict__ idx, float* __restrict__ wt, int T) {
+  __shared__ float sc[MOE_GROUPED_WARPS][MOE_GROUPED_MAX];
+  __shared__ float gs[MOE_GROUPED_WARPS][MOE_GROUPED_MAX];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * MOE_GROUPED_WARPS + warp;
+  if (t >= T) return;
+  const float* row = z + (size_t)t * ldz;
+  float* s = sc[warp];
+  float* g = gs[warp];
+  const int size = n_out / groups;
+  for (int e = lane; e < n_out; e += 32) s[e] = 1.0f / (1.0f + expf(-row[e]));
+  __syncwarp();
+  for (int k = lane; k < groups; k += 32) {
+    float a = -INFINITY, b = -INFINITY;     // the largest and the second
+    for (int e = k * size; e < (k + 1) * size; ++e) {
+      const float v = s[e];
+      if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+    }
+    g[k] = size > 1 ? a + b : a;
+  }
+  __syncwarp();
+  // the `keep` best groups stay; the others' scores are struck out
+  if (keep < groups) {
+    for (int round = 0; round < keep; ++round) {
+      float best = -INFINITY;
+      int best_k = 0x7fffffff;
+      for (int k = lane; k < groups; k += 32)
+        if (g[k] != INFINITY && g[k] > best) { best = g[k]; best_k = k; }   // k rises: a tie keeps the lower group
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int ok = __shfl_xor_sync(0xffffffffu, best_k, o);
+        if (ob > best || (ob == best && ok < best_k)) { best = ob; best_k = ok; }
+      }
+      if (lane == 0 && best_k < groups) g[best_k] = INFINITY;     // marks a kept group
+      __syncwarp();
+    }
+    for (int e = lane; e < n_out; e += 32)
+      if (g[e / size] != INFINITY) s[e] = -1.0f;                  // below every sigmoid
+    __syncwarp();
+  }
+  float sum = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < n_out; e += 32)
+      if (s[e] > best) { best = s[e]; best_e = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = best_e;
+      wt[(size_t)t * top + k] = best;
+      s[best_e] = -2.0f;
+    }
+    sum += best;
+    __syncwarp();
+  }
+  const float f = scale / (sum + 1e-20f);
+  for (int k = lane; k < top; k += 32) wt[(size_t)t * top + k] *= f;
+}
+
+extern "C" int TL_NAME(tl_moe_route_grouped)(const float* z, int ldz, int n_out, int groups, int keep, int top,
+                                             float scale, int* idx, float* wt, int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_out < 1 || groups < 1 || n_out % groups || keep < 1 || keep > groups || top < 1 ||
+      top > keep * (n_out / groups))
+    return TL_ERR_BAD_ARG;
+  if (n_out > MOE_GROUPED_MAX) return TL_ERR_UNSUPPORTED;
+  return tl_launch(moe_route_grouped_kernel, dim3((T + MOE_GROUPED_WARPS - 1) / MOE_GROUPED_WARPS),
+                   dim3(MOE_GROUPED_WARPS * 32), 0, stream, z, ldz, n_out, groups, keep, top, scale, idx, wt, T);
+}
+
 // Groups the pairs by expert.  offsets[e] .. offsets[e + 1] are the rows of expert e < E in the
 // grouped order; row_token[row] is the token a row belongs to; row_of[pair] is the row of pair
 // (t, k), or -1 for a pair whose expert hands its input through.  One block: the pairs of a step

@@ -136,7 +136,9 @@ class CoreOps:
                      "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan", "tl_gated_scan_groups",
                      "tl_stream_spread", "tl_stream_sum", "tl_hc_read_norm", "tl_hc_write", "tl_branch_norm_mean",
                      "tl_headnorm_silu_gate", "tl_qk_norm_cache_write", "tl_sink_attn", "tl_gla_scan", "tl_gla_scan_scratch",
-                     "tl_moe_route", "tl_moe_plan", "tl_moe_gemm", "tl_moe_combine"):
+                     "tl_moe_route", "tl_moe_plan", "tl_moe_gemm", "tl_moe_combine", "tl_moe_route_grouped",
+                     "tl_rotary_cache_write", "tl_diff_heads", "tl_sigmoid_gate", "tl_norm_add_norm", "tl_relu_squared",
+                     "tl_clamped_glu"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
             setattr(self, "_" + base, fn)
@@ -697,6 +699,119 @@ class CoreOps:
             _need(correction, torch.float32, "router correction")
         _check(self._tl_moe_route(_ptr(z), c_int(z.stride(0)), _ptr(correction), c_int(n_out), c_int(top), _ptr(idx),
                                   _ptr(wt), c_int(T), _stream()), "moe_route")
+
+    # ---- rotated queries and keys around the paged attention ----------------------------------------
+    def rotary_cache_write(self, z: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, style: int,
+                           unit_norm: bool, eps: float, q_out: torch.Tensor, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                           seq_slot: torch.Tensor, page_table: torch.Tensor, nq: int, nk: int, nv: int, dim: int,
+                           vdim: int, slots: int = 1) -> None:
+        """The projections `z` (32-bit rows: `nq` query vectors and `nk` key vectors of `dim`, then `nv` value
+        heads of `vdim`): the first `rot` entries of every query and key vector are rotated by the token's
+        position (`style` 0: pairs (i, i + rot/2), 1: pairs (2i, 2i + 1)), then, with `unit_norm`, the vector
+        is divided by its root mean square; q goes to `q_out`, k and v into the pages.  With `slots` > 1 a
+        key row of the pages holds `slots` key vectors side by side and query vector j becomes a row of that
+        width that is zero outside slot j % slots."""
+        _need(z, torch.float32, "projections", contiguous=False)
+        _need(q_out, self.act_dtype, "q out")
+        _need(k_pages, self.act_dtype, "k pages")
+        _need(v_pages, self.act_dtype, "v pages")
+        _need(page_table, torch.int32, "page table")
+        T = z.shape[0]
+        cols = (nq + nk) * dim + nv * vdim
+        width = slots * dim
+        if z.shape[1] < cols or z.stride(1) != 1 or q_out.shape != (T, nq * width) or nk != nv * slots or \
+                k_pages.shape[1:] != (nv, PAGE, width) or v_pages.shape[1:] != (nv, vdim, PAGE):
+            raise KernelError("rotary_cache_write: sizes do not match")
+        if rot:
+            _need(inv_freq, torch.float32, "inverse frequencies")
+            if inv_freq.numel() != rot // 2:
+                raise KernelError("rotary_cache_write: one inverse frequency per rotated pair is needed")
+        _check(self._tl_rotary_cache_write(
+            _ptr(z), c_int(z.stride(0)), _ptr(inv_freq if rot else None), c_int(rot), c_int(style),
+            c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(token_pos),
+            _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), c_int(T), c_int(nq),
+            c_int(nk), c_int(nv), c_int(dim), c_int(vdim), c_int(slots), _stream()), "rotary_cache_write")
+
+    def diff_heads(self, a: torch.Tensor, lam: float, eps: float, mult: float, out: torch.Tensor, heads: int,
+                   vdim: int) -> None:
+        """a: [T, heads * 2 * vdim] (two maps' outputs per head); out[t, h] = o / rms(o) * mult with
+        o = a[t, h, 0] - lam * a[t, h, 1]."""
+        _need(a, self.act_dtype, "attention maps")
+        _need(out, self.act_dtype, "difference of maps")
+        T = a.shape[0]
+        if a.shape != (T, heads * 2 * vdim) or out.shape != (T, heads * vdim):
+            raise KernelError("diff_heads: sizes do not match")
+        _check(self._tl_diff_heads(_ptr(a), c_float(lam), c_float(eps), c_float(mult), _ptr(out), c_int(T),
+                                   c_int(heads), c_int(vdim), _stream()), "diff_heads")
+
+    def sigmoid_gate(self, x: torch.Tensor, gate: torch.Tensor) -> None:
+        """x *= sigmoid(gate), entry by entry; gate 32-bit, rows may be strided."""
+        _need(x, self.act_dtype, "gated tensor")
+        _need(gate, torch.float32, "gate", contiguous=False)
+        if gate.shape != x.shape or gate.stride(1) != 1:
+            raise KernelError("sigmoid_gate: sizes do not match")
+        _check(self._tl_sigmoid_gate(_ptr(x), _ptr(gate), c_int(gate.stride(0)), c_int(x.shape[0]),
+                                     c_int(x.shape[1]), _stream()), "sigmoid_gate")
+
+    # ---- a block with a norm before and after each sublayer ------------------------------------------
+    def norm_add_norm(self, y: torch.Tensor, w_out: torch.Tensor, eps_out: float, x: torch.Tensor,
+                      w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0,
+                      xn: Optional[torch.Tensor] = None) -> None:
+        """x += y / rms(y) * w_out (32-bit stream, in place); with `w_next`, also xn = x / rms(x) * w_next in
+        the activation type."""
+        _need(y, torch.float32, "sublayer output", contiguous=False)
+        _need(x, torch.float32, "stream")
+        T, H = x.shape
+        if y.shape != (T, H) or y.stride(1) != 1 or w_out.numel() != H:
+            raise KernelError("norm_add_norm: sizes do not match")
+        w32 = w_out.dtype == torch.float32
+        if not w32 and w_out.dtype != torch.bfloat16:
+            raise KernelError("norm_add_norm: norm weights must be 32-bit or bfloat16")
+        if w_next is not None:
+            if w_next.dtype != w_out.dtype or w_next.numel() != H or xn is None:
+                raise KernelError("norm_add_norm: the next norm must match the first")
+            _need(xn, self.act_dtype, "normed stream")
+            if xn.shape != (T, H):
+                raise KernelError("norm_add_norm: sizes do not match")
+        _check(self._tl_norm_add_norm(_ptr(y), c_int(y.stride(0)), _ptr(w_out), _ptr(w_next), c_int(1 if w32 else 0),
+                                      c_float(eps_out), c_float(eps_next), _ptr(x), _ptr(xn), c_int(T), c_int(H),
+                                      _stream()), "norm_add_norm")
+
+    def relu_squared(self, z: torch.Tensor, out: torch.Tensor) -> None:
+        """out = max(z, 0)^2; z 32-bit, rows may be strided."""
+        _need(z, torch.float32, "pre-activations", contiguous=False)
+        _need(out, self.act_dtype, "activations")
+        if z.shape != out.shape or z.stride(1) != 1:
+            raise KernelError("relu_squared: sizes do not match")
+        _check(self._tl_relu_squared(_ptr(z), c_int(z.stride(0)), _ptr(out), c_int(out.shape[0]), c_int(out.shape[1]),
+                                     _stream()), "relu_squared")
+
+    def clamped_glu(self, z: torch.Tensor, limit: float, alpha: float, out: torch.Tensor) -> None:
+        """z: [T, 2 n] 32-bit, gate columns then up columns: g = min(g, limit), u = clamp(u, -limit, limit),
+        out = g * sigmoid(alpha g) * (u + 1)."""
+        _need(z, torch.float32, "pre-activations", contiguous=False)
+        _need(out, self.act_dtype, "activations")
+        T, n = out.shape
+        if z.shape != (T, 2 * n) or z.stride(1) != 1:
+            raise KernelError("clamped_glu: sizes do not match")
+        _check(self._tl_clamped_glu(_ptr(z), c_int(z.stride(0)), c_float(limit), c_float(alpha), _ptr(out), c_int(T),
+                                    c_int(n), _stream()), "clamped_glu")
+
+    def moe_route_grouped(self, z: torch.Tensor, groups: int, keep: int, top: int, scale: float, idx: torch.Tensor,
+                          wt: torch.Tensor) -> None:
+        """s = sigmoid(z[t]); only experts of the `keep` groups (of `groups` equal groups of neighbours) with
+        the largest sum of their two best s can be chosen; idx[t, :top] = the largest s among them (ties: the
+        lower index), wt = their s / (their sum + 1e-20) * scale."""
+        _need(z, torch.float32, "router logits", contiguous=False)
+        _need(idx, torch.int32, "chosen experts")
+        _need(wt, torch.float32, "expert weights")
+        T, n_out = z.shape
+        if z.stride(1) != 1 or idx.shape != (T, top) or wt.shape != (T, top):
+            raise KernelError("moe_route_grouped: sizes do not match")
+        _check(self._tl_moe_route_grouped(_ptr(z), c_int(z.stride(0)), c_int(n_out), c_int(groups), c_int(keep),
+                                          c_int(top), c_float(scale), _ptr(idx), _ptr(wt), c_int(T), _stream()),
+               "moe_route_grouped")
 
     def moe_plan(self, idx: torch.Tensor, experts: int, offsets: torch.Tensor, row_token: torch.Tensor,
                  row_of: torch.Tensor) -> None:

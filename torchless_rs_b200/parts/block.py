@@ -152,3 +152,80 @@ class BranchNormBlock:
 class BranchNormMixerBlock(BranchNormBlock):
     """The same block for a layer without a feed-forward: x <- x + m * norm_1(mixer(x))."""
     norm_roles = ("mixer_out_norm",)
+
+
+class NormedInput:
+    """What a sandwich block hands to the next one: the next block's first norm already applied to the
+    stream, written by the kernel that last changed the stream.  (`valid` is False so that a block that
+    expects the prepared input of a folded norm ignores it.)"""
+    valid = False
+
+    def __init__(self, xn: torch.Tensor, norm):
+        self.xn, self.norm = xn, norm
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """x <- x + N_1b(mixer(N_1(x))); x <- x + N_2b(feed_forward(N_2(x))): a norm before and after every
+    sublayer, each with its own weight.
+
+    A sublayer writes its output to a 32-bit buffer (one that says `can_overwrite` stores it, any other adds
+    into the zeroed buffer, so every registered mixer and feed-forward fits); one kernel norms that output,
+    adds it to the stream and applies the norm that comes next (this block's second, or the next block's
+    first, which is handed on as a `NormedInput`), so the stream crosses memory once per sublayer.  The
+    fused kernel takes norms with a plain weight per coordinate (`weight`, `eps`); the next norm is fused
+    only if its weight has the same type as this one's."""
+    norm_roles = ("mixer_norm", "mixer_out_norm", "feed_forward_norm", "feed_forward_out_norm")
+    takes_carry = True
+
+    def __init__(self, spec, rt: Runtime, mixer, feed_forward, norms):
+        self.rt = rt
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = dict(norms)
+
+    @property
+    def first_norm(self):
+        return self.norms["mixer_norm"]
+
+    def _sublayer(self, part, norm_in, norm_out, x, xn, batch, next_norm):
+        """x += norm_out(part(xn)); returns next_norm(x) if it could be taken along, else None."""
+        rt = self.rt
+        y = rt.workspace.get("branch_out", x.shape, torch.float32)
+        if getattr(part, "can_overwrite", False):
+            part.forward(xn, y, batch, overwrite=True)
+        else:
+            y.zero_()
+            part.forward(xn, y, batch)
+        fuse = (next_norm is not None and getattr(next_norm, "weight", None) is not None
+                and getattr(next_norm, "size", None) == x.shape[1]
+                and next_norm.weight.dtype == norm_out.weight.dtype)
+        if not fuse:
+            rt.ops.norm_add_norm(y, norm_out.weight, norm_out.eps, x)
+            return None
+        out = rt.workspace.get("block_normed", x.shape, rt.act_dtype)
+        rt.ops.norm_add_norm(y, norm_out.weight, norm_out.eps, x, next_norm.weight, next_norm.eps, out)
+        return out
+
+    def _input(self, norm, x, carry):
+        if isinstance(carry, NormedInput) and carry.norm is norm and carry.xn.shape == x.shape:
+            return carry.xn
+        return norm(x, self.rt.workspace.get("block_normed", x.shape, self.rt.act_dtype))
+
+    def forward(self, x: torch.Tensor, batch, carry=None, next_norm=None):
+        n = self.norms
+        xn = self._input(n["mixer_norm"], x, carry)
+        second = n.get("feed_forward_norm")
+        got = self._sublayer(self.mixer, n["mixer_norm"], n["mixer_out_norm"], x, xn, batch,
+                             second if second is not None else next_norm)
+        if second is None:
+            return NormedInput(got, next_norm) if got is not None else None
+        xn = got if got is not None else second(x, self.rt.workspace.get("block_normed", x.shape, self.rt.act_dtype))
+        got = self._sublayer(self.feed_forward, second, n["feed_forward_out_norm"], x, xn, batch, next_norm)
+        return NormedInput(got, next_norm) if got is not None else None
+
+
+@register_block("sandwich_mixer_only")
+class SandwichMixerBlock(SandwichBlock):
+    """The same block for a layer without a feed-forward: x <- x + N_1b(mixer(N_1(x)))."""
+    norm_roles = ("mixer_norm", "mixer_out_norm")

@@ -121,3 +121,37 @@ class NoFeedForward:
 
     def forward(self, xn, residual, batch, emit=None) -> None:
         pass
+
+
+@register_feed_forward("relu_squared")
+class ReluSquaredFeedForward:
+    """down( max(up x, 0)^2 ).  Parameters: `hidden_size`, `intermediate_size`.  Tensors under the prefix:
+    up, down."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.prefix = prefix
+        self.rt = rt
+        self.matmul = Matmul(rt)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
+        h, i = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        return {f"{prefix}.up": TensorSpec((i, h)), f"{prefix}.down": TensorSpec((h, i))}
+
+    def load(self, weights: Dict[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.w_up = self.rt.matrix(weights[f"{p}.up"])
+        self.w_down = self.rt.matrix(weights[f"{p}.down"])
+
+    def forward(self, xn, residual: torch.Tensor, batch, emit=None, overwrite: bool = False) -> None:
+        rt, ws = self.rt, self.rt.workspace
+        T = residual.shape[0]
+        z = ws.get("ffn_pre", (T, self.inter), torch.float32)
+        self.matmul(xn, self.w_up, z, ops.MODE_STORE_F32)
+        act = ws.get("ffn_act", (T, self.inter), rt.act_dtype)
+        rt.ops.relu_squared(z, act)
+        self.matmul(act, self.w_down, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)

@@ -14,7 +14,8 @@ from .runtime import Runtime
 
 @register_norm("rmsnorm")
 class RMSNorm:
-    """Parameters: `size`, `eps`.  Interface of every norm: `expected_tensors(spec, prefix)` (a class method),
+    """Parameters: `size`, `eps`; optionally `bare_name` (the weight is stored under the norm's own name,
+    without `.weight`).  Interface of every norm: `expected_tensors(spec, prefix)` (a class method),
     `load(weights)`, and `__call__(x, out, rows=None)` from the 32-bit stream to an
     activation tensor; `rows` (int32, on the device) picks input rows."""
 
@@ -23,13 +24,14 @@ class RMSNorm:
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
-        self.name = f"{prefix}.weight"
+        self.name = prefix if spec.params.get("bare_name") else f"{prefix}.weight"
         self.rt = rt
         self.weight: Optional[torch.Tensor] = None
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
-        return {f"{prefix}.weight": TensorSpec((int(spec.params["size"]),))}
+        name = prefix if spec.params.get("bare_name") else f"{prefix}.weight"
+        return {name: TensorSpec((int(spec.params["size"]),))}
 
     def load(self, weights: Dict[str, torch.Tensor]) -> None:
         self.weight = self.rt.vector(weights[self.name])

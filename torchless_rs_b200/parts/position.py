@@ -28,3 +28,9 @@ class RotaryHalfSplit:
         i = torch.arange(half, dtype=torch.float64)
         inv = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), i / half)
         self.inv_freq = inv.to(torch.float32).to(rt.device)
+
+
+@register_position("rope_interleaved")
+class RotaryInterleaved(RotaryHalfSplit):
+    """The same frequencies with neighbouring pairs: dimension 2i turns with dimension 2i + 1."""
+    style = STYLE_INTERLEAVED
