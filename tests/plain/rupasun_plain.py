@@ -38,6 +38,8 @@ def rotate(x: np.ndarray, positions: np.ndarray, dims: int, base: float, interle
     """x: [n, heads, size].  The first `dims` entries of every head are turned by the angle
     position * base^(-2i/dims) in pairs (i, i + dims/2), or (2i, 2i + 1) if `interleaved`; the rest pass."""
     out = x.copy()
+    if not dims:
+        return out
     half = dims // 2
     freq = base ** (-2.0 * np.arange(half) / dims)
     a = positions[:, None, None] * freq[None, None, :]
@@ -75,7 +77,7 @@ def differential_attention(h: np.ndarray, w: dict, p: dict, eps: float, position
     n = h.shape[0]
     positions = np.arange(n, dtype=np.float64) if positions is None else positions
     H, G, dim, vdim = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
-    rot = p["rot"]
+    rot = p.get("rot") or {"dims": 0, "base": 1.0}
     # rows head by head, within a head map 1 then map 2: [n, heads * 2, dim]
     q = rotate((h @ w["q"].T).reshape(n, H * 2, dim), positions, rot["dims"], rot["base"], False).reshape(n, H, 2, dim)
     k = rotate((h @ w["k"].T).reshape(n, G * 2, dim), positions, rot["dims"], rot["base"], False).reshape(n, G, 2, dim)
@@ -94,7 +96,7 @@ def window_attention(h: np.ndarray, w: dict, p: dict, eps: float, positions=None
     n = h.shape[0]
     positions = np.arange(n, dtype=np.float64) if positions is None else positions
     H, G, dim, vdim = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
-    rot = p["rot"]
+    rot = p.get("rot") or {"dims": 0, "base": 1.0}
     q = rms_normalise(rotate((h @ w["q"].T).reshape(n, H, dim), positions, rot["dims"], rot["base"], True), eps)
     k = rms_normalise(rotate((h @ w["k"].T).reshape(n, G, dim), positions, rot["dims"], rot["base"], True), eps)
     v = (h @ w["v"].T).reshape(n, G, vdim)
