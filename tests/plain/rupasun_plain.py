@@ -137,10 +137,29 @@ def route(scores: np.ndarray, top: int, groups: int, keep: int):
     return np.argsort(-masked, kind="stable")[:top], allowed
 
 
-def expert_ff(h: np.ndarray, w: dict, p: dict) -> np.ndarray:
+def route_margin(scores: np.ndarray, top: int, groups: int, keep: int) -> float:
+    """How far the scores of one token are from another choice: the smaller of the gap between the last
+    kept and the first dropped group's score (halved: it is a sum of two scores) and the gap between the
+    last chosen and the first not chosen score among the allowed experts."""
+    E = scores.shape[0]
+    _, allowed = route(scores, top, groups, keep)
+    margin = np.inf
+    if keep < groups:
+        g = np.sort(np.sort(scores.reshape(groups, E // groups), axis=1)[:, ::-1][:, :2].sum(axis=1))[::-1]
+        margin = min(margin, (g[keep - 1] - g[keep]) / 2.0)
+    if top < allowed.sum():
+        a = np.sort(scores[allowed])[::-1]
+        margin = min(margin, a[top - 1] - a[top])
+    return float(margin)
+
+
+def expert_ff(h: np.ndarray, w: dict, p: dict, margins: list | None = None) -> np.ndarray:
+    """`margins`, if given, receives one array [n] of `route_margin` per call."""
     r, e = p["router"], p["expert"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
     s = sigmoid(h @ w["router"].T)
+    if margins is not None:
+        margins.append(np.array([route_margin(s[t], r["top"], groups["count"], groups["keep"]) for t in range(h.shape[0])]))
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         chosen, _ = route(s[t], r["top"], groups["count"], groups["keep"])
@@ -153,8 +172,8 @@ def expert_ff(h: np.ndarray, w: dict, p: dict) -> np.ndarray:
     return out
 
 
-def feed_forward(h: np.ndarray, w: dict, p: dict) -> np.ndarray:
-    return dense_ff(h, w) if p["kind"] == "dense" else expert_ff(h, w, p)
+def feed_forward(h: np.ndarray, w: dict, p: dict, margins: list | None = None) -> np.ndarray:
+    return dense_ff(h, w) if p["kind"] == "dense" else expert_ff(h, w, p, margins)
 
 
 MIXERS = {"attention": differential_attention, "attention_2": window_attention}
@@ -164,8 +183,9 @@ def sub(weights: dict, prefix: str) -> dict:
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, weights: dict, tokens, return_layers: bool = False, dtype=np.float64):
-    """Logits [n, vocab] of one sequence from its first token (and the stream after every layer)."""
+def forward(cfg: dict, weights: dict, tokens, return_layers: bool = False, dtype=np.float64, margins: list | None = None):
+    """Logits [n, vocab] of one sequence from its first token (and the stream after every layer).
+    `margins` receives every expert layer's `route_margin` per position."""
     W = {k: np.asarray(v, dtype=dtype) if np.asarray(v).dtype.kind == "f" else np.asarray(v) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     x = W["embed"][np.asarray(tokens)]
@@ -175,7 +195,7 @@ def forward(cfg: dict, weights: dict, tokens, return_layers: bool = False, dtype
         y = MIXERS[l["type"]](norm(x, W[p + "norm1"], eps), sub(W, p + "mix."), l["mixer"], eps)
         x = x + norm(y, W[p + "norm1b"], eps)
         if l.get("mlp"):
-            y = feed_forward(norm(x, W[p + "norm2"], eps), sub(W, p + "mlp."), l["mlp"])
+            y = feed_forward(norm(x, W[p + "norm2"], eps), sub(W, p + "mlp."), l["mlp"], margins)
             x = x + norm(y, W[p + "norm2b"], eps)
         streams.append(x.copy())
     logits = norm(x, W["final.norm"], eps) @ W["head"].T

@@ -186,3 +186,23 @@ class TModel:
 
 def tokens_of(rng, n, vocab):
     return [int(t) for t in rng.integers(0, vocab, size=n)]
+
+
+def sure_tokens(tm: "TModel", rng, n: int, margin: float | None = None):
+    """`n` random tokens none of which leaves a router within `margin` of another choice (by default what
+    the rounding of the router's input to the model's activation type can move: a token that does would
+    run through other experts than in the plain implementation, and every later token would see it).
+    A position's routers depend on the tokens up to it only, so the first close position gets another
+    token until none is left."""
+    if margin is None:
+        margin = 1e-4 if tm.dtype == "float32" else 2e-2
+    V = tm.cfg["vocab"]
+    toks = tokens_of(rng, n, V)
+    for _ in range(20 * n):
+        m: list = []
+        plain.forward(tm.cfg, tm.weights, toks, margins=m)
+        close = np.nonzero(np.min(np.stack(m), axis=0) < margin)[0] if m else []
+        if len(close) == 0:
+            return toks
+        toks[int(close[0])] = int(rng.integers(0, V))
+    raise AssertionError("no sequence without a close call was found")
