@@ -280,7 +280,7 @@ def reference_arm(args) -> int:
 
 
 def design_arm(args) -> int:
-    """`--design kikopel|tovapel`: prefill and decode throughput of that design at layer sizes of a real
+    """`--design kikopel|tovapel|rupasun`: prefill and decode throughput of that design at layer sizes of a real
     model (random weights), beside Mistral (the closest existing model) at equal width, heads, layers,
     feed-forward and window, and every kernel of the design alone against its roofline beside the like
     kernel of the Mistral path.  One JSON line; the default workload is not touched."""
@@ -292,9 +292,11 @@ def design_arm(args) -> int:
     size, L = args.design_size, args.layers or 8
     T, B, ctx = PREFILL_TOKENS, args.batch or 8, 2048
     design = args.design
-    sizes = {"kikopel": measure.KIKOPEL_SIZES, "tovapel": measure.TOVAPEL_SIZES}[design]
+    sizes = {"kikopel": measure.KIKOPEL_SIZES, "tovapel": measure.TOVAPEL_SIZES,
+             "rupasun": measure.RUPASUN_SIZES}[design]
     configs = {"kikopel": (measure.kikopel_config, measure.mistral_like, measure.kikopel_kernels),
-               "tovapel": (measure.tovapel_config, measure.tovapel_like, measure.tovapel_kernels)}[design]
+               "tovapel": (measure.tovapel_config, measure.tovapel_like, measure.tovapel_kernels),
+               "rupasun": (measure.rupasun_config, measure.rupasun_like, measure.rupasun_kernels)}[design]
     out = {"design": design, "sizes": dict(sizes[size]), "layers": L, "dtype": "bf16",
            "data": "synthetic: random weights, fixed token ids", "prefill_tokens": T, "decode_batch": B,
            "decode_context": ctx, "steps": args.steps, "warmup": args.warmup}
@@ -340,7 +342,7 @@ def design_arm(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["kikopel", "tovapel"],
+    ap.add_argument("--design", default=None, choices=["kikopel", "tovapel", "rupasun"],
                     help="measure another design beside Mistral at equal sizes instead of the default workload")
     ap.add_argument("--design-size", default="1b", choices=["1b", "7b"])
     ap.add_argument("--gpus", type=int, default=1)

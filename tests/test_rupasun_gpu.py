@@ -613,3 +613,33 @@ def test_activations_of_the_feed_forwards(dtype):
     o.sigmoid_gate(xd, _dev(gate)[:, 4:])
     ref = x.double().numpy() * plain.sigmoid(gate[:, 4:].astype(np.float64))
     assert np.abs(xd.float().cpu().numpy() - ref).max() <= max(tol, 2e-6) * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (8, 1408, 2048), (40, 384, 4096), (100, 512, 1024), (130, 640, 512),
+                                   (200, 4096, 2048), (300, 1024, 256), (700, 1408, 1024), (2048, 2816, 1024)])
+def test_products_apply_the_activations_in_their_epilogues(M, N, K):
+    """The tensor-core product with the squared relu and with the clamped gate in its epilogue, on every
+    one of its kernels (few tokens with and without a K split, single SMs, pairs), against 64-bit sums
+    of the same bfloat16 inputs; limits that cut many of the values, and one that cuts none."""
+    from torchless_rs_b200.csrc import ops
+    from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
+    gm = GemmBf16.get()
+    rng = np.random.default_rng(M + N)
+    a = torch.as_tensor(rng.normal(0, 1.0, (M, K)), dtype=torch.float32).bfloat16()
+    w = torch.as_tensor(rng.normal(0, K ** -0.5, (2 * N, K)), dtype=torch.float32).bfloat16()
+    z = a.double().numpy() @ w.double().numpy().T
+    out = torch.zeros((M, N), dtype=torch.bfloat16).cuda()
+    assert gm.run(a.cuda(), w[:N].cuda(), out, ops.MODE_STORE_ACT, act=(ops.ACT_RELU_SQUARED,))
+    ref = np.maximum(z[:, :N], 0.0) ** 2
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= 1e-2 * np.abs(ref).max()
+    assert gm.run(a.cuda(), w[:N].cuda(), out, ops.MODE_STORE_ACT)            # and the plain mode is what it was
+    assert np.abs(out.float().cpu().numpy() - z[:, :N]).max() <= 1e-2 * np.abs(z).max()
+    for limit in (0.4, 1.0, 50.0):
+        assert gm.run(a.cuda(), w.cuda(), out, ops.MODE_SWIGLU, act=(ops.ACT_CLAMPED_GLU, limit, 1.702))
+        g, u = np.minimum(z[:, :N], limit), np.clip(z[:, N:], -limit, limit)
+        ref = g * plain.sigmoid(1.702 * g) * (u + 1.0)
+        assert np.abs(out.float().cpu().numpy() - ref).max() <= 1e-2 * np.abs(ref).max(), limit
+    assert gm.run(a.cuda(), w.cuda(), out, ops.MODE_SWIGLU)
+    ref = z[:, :N] * plain.sigmoid(z[:, :N]) * z[:, N:]
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= 1e-2 * np.abs(ref).max()
+    assert gm.take_error() == 0

@@ -8,7 +8,7 @@ from ctypes import byref, c_float, c_int, c_void_p
 import torch
 
 from . import build
-from .ops import KernelError, _check, _ptr, _stream, register_error_word
+from .ops import ACT_PLAIN, KernelError, _check, _ptr, _stream, register_error_word
 
 build.register_library("gemm_tc", ("gemm_tc.cu",), ())
 
@@ -36,8 +36,9 @@ class GemmBf16:
         self.lib.tl_gemm_tc.restype = c_int
         # declared once, so that a call passes plain numbers (no ctypes object per argument)
         P, I = c_void_p, c_int
-        self.lib.tl_gemm_tc.argtypes = [P, I, P, I, P, I, I, I, I, I, I, P, I, I, c_float, P, P, I, P,
-                                        ctypes.POINTER(c_int), P, ctypes.POINTER(c_int), P]
+        self.lib.tl_gemm_tc_act.restype = c_int
+        self.lib.tl_gemm_tc_act.argtypes = [P, I, P, I, P, I, I, I, I, I, I, P, I, I, c_float, P, P, I, P,
+                                            ctypes.POINTER(c_int), P, ctypes.POINTER(c_int), I, c_float, c_float, P]
         self.lib.tl_gemm_tc_take_error.restype = c_int
         register_error_word("gemm_tc", self.take_error)
         self._scratch = {}
@@ -49,14 +50,16 @@ class GemmBf16:
         return self._scratch[key]
 
     def run(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
-            scaled=None, emit=None, rope: "RopeArgs" = None) -> bool:
+            scaled=None, emit=None, rope: "RopeArgs" = None, act=None) -> bool:
         """out (op)= a @ w.T.  Returns False for shapes this kernel does not take.
 
         `scaled`: a `NormCarry` whose `xw` is `a`; outputs are scaled by each row's
         1/rms from its partial sums.  `emit`: (norm weight, NormCarry) for mode 1: if the
         kernel can, it fills the carry with the next norm's input and sets `carry.valid`.
         `rope`: for the q/k/v product (mode 0): if the kernel can, it rotates and writes q, k
-        and v itself instead of `out`; `self.rope_applied` says whether it did."""
+        and v itself instead of `out`; `self.rope_applied` says whether it did.
+        `act`: (ACT_RELU_SQUARED,) for mode 3, (ACT_CLAMPED_GLU, limit, alpha) for mode 2: what the
+        32-bit sums go through before they are rounded instead of the mode's own operation."""
         self.rope_applied = False
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             return False
@@ -77,14 +80,16 @@ class GemmBf16:
             if not t.is_cuda:
                 raise KernelError("kernel argument is not on a CUDA device; this package has no CPU path")
         addr = lambda t: t.data_ptr() if t is not None else None
-        st = self.lib.tl_gemm_tc(
+        kind, limit, alpha = (tuple(act) + (0.0, 0.0))[:3] if act else (ACT_PLAIN, 0.0, 0.0)
+        st = self.lib.tl_gemm_tc_act(
             a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K, mode, sms,
             addr(ss_in), scaled.tiles if scaled is not None else 0, scaled.size if scaled is not None else 0,
             scaled.eps if scaled is not None else 0.0,
             addr(carry.xw if carry is not None else None), addr(nw),
             1 if (nw is not None and nw.dtype == torch.float32) else 0,
             addr(carry.ss if carry is not None else None), byref(emitted),
-            ctypes.cast(byref(rope), c_void_p) if rope is not None else None, byref(applied), _stream())
+            ctypes.cast(byref(rope), c_void_p) if rope is not None else None, byref(applied),
+            kind, limit, alpha, _stream())
         if st == -2:
             return False
         _check(st, "gemm_tc")

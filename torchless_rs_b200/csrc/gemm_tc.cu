@@ -168,6 +168,10 @@ __device__ __forceinline__ float4 ld_remote_f32x4(uint32_t local_saddr, uint32_t
 }
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// What the epilogue applies before it rounds to the activation type (GemmArgs::act).
+#define ACT_PLAIN 0         // mode 3: the value; mode 2: silu(g) * u
+#define ACT_RELU_SQUARED 1  // mode 3: max(v, 0)^2
+#define ACT_CLAMPED_GLU 2   // mode 2: g = min(g, limit), u = clamp(u, -limit, limit): g * sigmoid(alpha g) * (u + 1)
 
 // ---------------------------------------------------------------------------
 // The kernel.  grid = (tiles of 128 weight rows, tiles of BN tokens, K splits).
@@ -176,6 +180,8 @@ struct GemmArgs {
   void* C;
   int ldc, M, N, K, mode, kb_per_split, stages;
   int raster;      // pair kernel: weight strips per group of the tile order (0: strip by strip)
+  int act;         // ACT_*
+  float act_limit, act_alpha;
   // Norm folded into the products around it (see the launcher's text).
   const float* ss_in;       // [M, ss_in_tiles] partial sums of squares of the input rows, or null
   int ss_in_tiles, norm_h;
@@ -196,6 +202,19 @@ struct GemmArgs {
   const int* rope_table;    // page table
   const float* rope_inv_freq;   // [hd / 2] or null
 };
+
+__device__ __forceinline__ float glu_f(const GemmArgs& a, float g, float u) {
+  if (a.act == ACT_CLAMPED_GLU) {
+    g = fminf(g, a.act_limit);
+    u = fminf(fmaxf(u, -a.act_limit), a.act_limit);
+    return g / (1.0f + expf(-a.act_alpha * g)) * (u + 1.0f);
+  }
+  return silu_f(g) * u;
+}
+__device__ __forceinline__ float act_f(const GemmArgs& a, float v) {
+  if (a.act == ACT_RELU_SQUARED) { v = fmaxf(v, 0.0f); return v * v; }
+  return v;
+}
 
 // The tail of a block's shared memory, after the stages: barriers and flags (256 bytes), the
 // per-warp sums of squares of the fold (1 KB), the tokens' 1/rms (1 KB) and, for token tiles
@@ -403,9 +422,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (j >= valid) break;
               const float sc = args.ss_in ? rinv_s[c0 + j] : 1.0f;
               const float v = __uint_as_float(r[j]) * sc;
-              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(v) * (__uint_as_float(u[j]) * sc));
+              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(glu_f(args, v, __uint_as_float(u[j]) * sc));
               else if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
-              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
+              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(act_f(args, v));
             }
           }
         }
@@ -564,8 +583,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             } else if (live4) {
               if (SWIGLU) {
                 uint2 o;
-                o.x = pack_bf16x2(silu_f(val[0]) * up[0], silu_f(val[1]) * up[1]);
-                o.y = pack_bf16x2(silu_f(val[2]) * up[2], silu_f(val[3]) * up[3]);
+                o.x = pack_bf16x2(glu_f(args, val[0], up[0]), glu_f(args, val[1], up[1]));
+                o.y = pack_bf16x2(glu_f(args, val[2], up[2]), glu_f(args, val[3], up[3]));
                 *reinterpret_cast<uint2*>((__nv_bfloat16*)args.C + idx) = o;
               } else if (args.mode == MODE_STORE_F32) {
                 *reinterpret_cast<float4*>((float*)args.C + idx) = make_float4(val[0], val[1], val[2], val[3]);
@@ -583,8 +602,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                 }
               } else {
                 uint2 o;
-                o.x = pack_bf16x2(val[0], val[1]);
-                o.y = pack_bf16x2(val[2], val[3]);
+                o.x = pack_bf16x2(act_f(args, val[0]), act_f(args, val[1]));
+                o.y = pack_bf16x2(act_f(args, val[2]), act_f(args, val[3]));
                 *reinterpret_cast<uint2*>((__nv_bfloat16*)args.C + idx) = o;
               }
             }
@@ -643,7 +662,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           const size_t idx = (size_t)(m0 + c) * args.ldc + n;
           float sq = 0.0f;
           if (live) {
-            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(val) * up);
+            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(glu_f(args, val, up));
             else if (args.rope_on) {
               // this column is dimension d of head `head`; rotate q and k at the token's position
               // (angle, sine and cosine in 32-bit) and write q, or k and v into the token's page
@@ -681,7 +700,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                 args.xw_out[(size_t)(m0 + c) * args.N + n] = __float2bfloat16_rn(cn * w);
                 sq = cn * cn;
               }
-            } else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(val);
+            } else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(act_f(args, val));
           }
           if (args.xw_out) {   // sum of squares of this tile's 128 columns, in a fixed order
 #pragma unroll
@@ -842,9 +861,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w,
             for (int j = 0; j < 16; ++j) {
               if (j >= valid) break;
               const float v = __uint_as_float(r[j]);
-              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(v) * __uint_as_float(u[j]));
+              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(glu_f(args, v, __uint_as_float(u[j])));
               else if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
-              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
+              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(act_f(args, v));
             }
           }
         }
@@ -1150,7 +1169,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
               const float other = theirs[j * 64 + col];
               const float g = up_half ? other : __uint_as_float(r[j]);
               const float u = up_half ? __uint_as_float(r[8 + j]) : other;
-              cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(g) * u);
+              cb[(size_t)j * args.ldc] = __float2bfloat16_rn(glu_f(args, g, u));
             }
           }
         }
@@ -1209,7 +1228,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
               if (j >= valid) break;
               const float v = __uint_as_float(r[j]);
               if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
-              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
+              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(act_f(args, v));
             }
           }
         }
@@ -1461,17 +1480,22 @@ struct TlRopeArgs {
 // query, key and value heads, are rotated at each token's position and written to q_out and
 // into the token's cache page, and *rope_applied = 1.  Otherwise *rope_applied = 0 and the
 // caller runs the rotation kernel on C.
-extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
-                          int N, int K, int mode, int num_sms, const float* ss_in, int ss_in_tiles,
-                          int norm_h, float eps_in, void* xw_out, const void* nw, int nw_is_f32,
-                          float* ss_out, int* emitted, const void* rope, int* rope_applied,
-                          cudaStream_t stream) {
+//
+// `act` (ACT_*), with its two constants: what modes 2 and 3 apply to the 32-bit sums before they round.
+extern "C" int tl_gemm_tc_act(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
+                              int N, int K, int mode, int num_sms, const float* ss_in, int ss_in_tiles,
+                              int norm_h, float eps_in, void* xw_out, const void* nw, int nw_is_f32,
+                              float* ss_out, int* emitted, const void* rope, int* rope_applied,
+                              int act, float act_limit, float act_alpha, cudaStream_t stream) {
   if (emitted) *emitted = 0;
   if (rope_applied) *rope_applied = 0;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
     return -2;
   if (mode < 0 || mode > 3) return -1;
+  if (act != ACT_PLAIN && !(act == ACT_RELU_SQUARED && mode == MODE_STORE_ACT) &&
+      !(act == ACT_CLAMPED_GLU && mode == MODE_SWIGLU))
+    return -1;
   const bool swiglu = mode == MODE_SWIGLU;
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
@@ -1541,6 +1565,7 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
         make_map(&px, X, M, K, ldx, pair_bn / 2)) {
       GemmArgs p = {};
       p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.mode = mode;
+      p.act = act; p.act_limit = act_limit; p.act_alpha = act_alpha;
       // many token tiles: strips of weights in groups of 8, so that a wave of pairs works on 8 strips and 9
       // token tiles instead of 2 or 3 strips and every token tile, whose activations then no longer fit
       // the L2 cache (measured at 8192 tokens: down 774 -> 699 us, gate-up 1497 -> 1375 us, q/k/v 311 -> 281
@@ -1558,6 +1583,7 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   GemmArgs a;
   a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
   a.mode = mode; a.kb_per_split = kb_per_split; a.stages = 0;
+  a.act = act; a.act_limit = act_limit; a.act_alpha = act_alpha;
   a.ss_in = ss_in; a.ss_in_tiles = ss_in_tiles; a.norm_h = norm_h; a.eps_in = eps_in;
   // the fold and the rotation live in the few-token kernel's K-split reduction only: the
   // persistent kernels neither write xw_out / ss_out nor look at the rope arguments
@@ -1596,6 +1622,15 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
     default: DISPATCH(256);
   }
 #undef DISPATCH
+}
+
+extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
+                          int N, int K, int mode, int num_sms, const float* ss_in, int ss_in_tiles,
+                          int norm_h, float eps_in, void* xw_out, const void* nw, int nw_is_f32,
+                          float* ss_out, int* emitted, const void* rope, int* rope_applied,
+                          cudaStream_t stream) {
+  return tl_gemm_tc_act(X, ldx, W, ldw, C, ldc, M, N, K, mode, num_sms, ss_in, ss_in_tiles, norm_h, eps_in, xw_out,
+                        nw, nw_is_f32, ss_out, emitted, rope, rope_applied, ACT_PLAIN, 0.0f, 0.0f, stream);
 }
 
 // Reads and clears the error word that a kernel sets when one of its bounded waits ran

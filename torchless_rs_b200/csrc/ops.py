@@ -17,6 +17,8 @@ MODE_STORE_F32 = 0
 MODE_ACCUM_F32 = 1
 MODE_SWIGLU = 2
 MODE_STORE_ACT = 3
+# what the tensor-core product's modes 2 and 3 can apply before rounding instead of their own operation
+ACT_PLAIN, ACT_RELU_SQUARED, ACT_CLAMPED_GLU = 0, 1, 2
 
 PAGE = build.PAGE_TOKENS  # tokens per cache page; the kernels are compiled with the same number
 

@@ -501,6 +501,204 @@ def tovapel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
     return rows
 
 
+# A decoder whose sublayers stand between two norms; differential attention (two maps of 64 per head over
+# values of 128) and gated window attention (heads of 128, half of them rotated, unit-normed, capped) in
+# turn; a squared-relu feed-forward of one and a half times the SwiGLU inner size (equal weights) and, every
+# other layer, sixteen clamped experts in four groups of which two are kept, four chosen, plus a shared expert.
+RUPASUN_SIZES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, d_dim=64, dim=128, vdim=128, window=4096, like_ff=5632, ff=8448,
+               experts=16, groups=4, keep=2, top=4, e_ff=1408, vocab=32000),
+    "7b": dict(width=4096, heads=32, kv_heads=8, d_dim=64, dim=128, vdim=128, window=4096, like_ff=14336, ff=21504,
+               experts=16, groups=4, keep=2, top=4, e_ff=3584, vocab=32000),
+}
+
+
+def rupasun_config(size: str, layers: int) -> dict:
+    """config.json of a Rupasun model of `layers` layers at these sizes: the two mixers in turn, dense and
+    expert feed-forwards in turn at half that pace (so every pairing occurs)."""
+    z = RUPASUN_SIZES[size]
+    diff = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["d_dim"], "vdim": z["vdim"],
+            "scale": 1.0 / math.sqrt(z["d_dim"]), "diff": 0.2, "rot": {"dims": z["d_dim"], "base": 10000.0}}
+    win = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": 1.0,
+           "softcap": 50.0, "mask": {"size": z["window"]}, "rot": {"dims": z["dim"] // 2, "base": 10000.0}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["e_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5,
+                      "groups": {"count": z["groups"], "keep": z["keep"]}},
+           "shared": {"ff": z["e_ff"], "limit": 7.0}}
+    return {"architecture": "Rupasun", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-5},
+            "max_position_embeddings": 32768,
+            "layers": [{"type": "attention_2" if i % 2 else "attention", "mixer": win if i % 2 else diff,
+                        "mlp": moe if (i // 2) % 2 else dense} for i in range(layers)]}
+
+
+def rupasun_like(size: str, layers: int) -> dict:
+    """The closest existing model at equal size: Mistral with the same width, heads, key/value heads and
+    window, and a SwiGLU feed-forward of the dense layers' weight."""
+    z = RUPASUN_SIZES[size]
+    return dict(MISTRAL_7B_SIZES, num_hidden_layers=layers, hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=128, intermediate_size=z["like_ff"],
+                vocab_size=z["vocab"], sliding_window=z["window"], max_position_embeddings=32768)
+
+
+def rupasun_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) -> list:
+    """Every kernel of the Rupasun design alone at the sizes `size`, for a prompt of T tokens and for a decode
+    step of B sequences at a context of `ctx`, beside the like kernel of an existing model at equal sizes.
+    Rows and roofline as `kikopel_kernels` defines them.  (The experts' grouped products, their plan and their
+    weighted sum are the kernels that `tovapel_kernels` measures, at the same sizes.)"""
+    import json
+    import os
+    from .csrc import ops
+    from .csrc.attention_bf16 import AttentionBf16
+    from .csrc.gemm_bf16 import GemmBf16
+    from .parts.runtime import Workspace
+    from .parts.sink_attention import run_attention
+    z = RUPASUN_SIZES[size]
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.isfile(pk):
+        peaks.update(json.load(open(pk)))
+    o = ops.core_ops(torch.bfloat16)
+    dev, bf = "cuda", torch.bfloat16
+    H, G, dd, dim, vdim, W = z["heads"], z["kv_heads"], z["d_dim"], z["dim"], z["vdim"], z["width"]
+    rows = []
+
+    def report(name, case, us, byts, flops):
+        t_mem, t_fl = byts / (peaks["hbm_gbs"] * 1e3), flops / (peaks["bf16_tflops"] * 1e6)     # microseconds
+        frac = max(t_mem, t_fl) / us
+        rows.append({"kernel": name, "case": case, "us": round(us, 2), "roofline_frac": round(frac, 4),
+                     "bound": "memory" if t_mem >= t_fl else "tensor"})
+        print(f"{name:34s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})", file=file)
+
+    ws = Workspace(torch.device("cuda"))
+    gm = GemmBf16.get()
+    for case, n_tok, seqs, past in ((f"prompt {T}", T, 1, 0), (f"decode {B} x {ctx}", B, B, ctx - 1)):
+        per = n_tok // seqs
+        few = max(2, iters // 8) if n_tok > 64 else iters
+        pos = torch.cat([torch.arange(past, past + per, dtype=torch.int32) for _ in range(seqs)]).to(dev)
+        seq = torch.arange(seqs, dtype=torch.int32).repeat_interleave(per).to(dev)
+        start = (torch.arange(seqs + 1, dtype=torch.int32) * per).to(dev)
+        lens = torch.full((seqs,), past + per, dtype=torch.int32, device=dev)
+        seen_all = sum(p + 1 for p in range(past, past + per)) * seqs
+        seen_win = sum(min(p + 1, z["window"]) for p in range(past, past + per)) * seqs
+        kp, vp, table, slot = _paged(seqs, past + per, G, 128)
+
+        class _B:      # what the kernel choice reads of a step
+            n_tokens, n_seqs, is_decode, max_len, seq_start, seq_len, seq_slot = n_tok, seqs, per == 1, past + per, start, lens, slot
+        # --- differential attention: 2 H query rows of two maps' width over G key rows; then the difference
+        wd = 2 * dd
+        kd = kp if wd == 128 else _paged(seqs, past + per, G, wd)[0]
+        q2 = torch.randn((n_tok, 2 * H * wd), device=dev, dtype=bf)
+        maps = torch.empty((n_tok, 2 * H * vdim), device=dev, dtype=bf)
+        us = _time(lambda: run_attention(o, q2, kd, vp, None, None, maps, pos, seq, slot, table, 2 * H, G, wd, vdim,
+                                         None, 0, dd ** -0.5, None, _B, ws), few)
+        cache_d = 2.0 * seqs * (past + per) * G * (wd + vdim)
+        report("attention (two maps)", case, us, cache_d + n_tok * 2 * H * (wd + vdim) * 2.0,
+               2.0 * 2 * H * (dd + vdim) * seen_all)
+        q = torch.randn((n_tok, H * dim), device=dev, dtype=bf)
+        out = torch.empty((n_tok, H * vdim), device=dev, dtype=bf)
+        us = _time(lambda: run_attention(o, q, kp, vp, None, None, out, pos, seq, slot, table, H, G, dim, vdim,
+                                         z["window"], 0, 1.0, 50.0, _B, ws), few)
+        cache_w = 2.0 * seqs * min(past + per, z["window"]) * G * (dim + vdim)
+        report("attention (window, cap)", case, us, cache_w + n_tok * H * (dim + vdim) * 2.0,
+               2.0 * H * (dim + vdim) * seen_win)
+        att = AttentionBf16.get(128)
+        om = torch.empty_like(q)
+        if seqs == 1:
+            us = _time(lambda: att.prefill(q, kp, vp, om, start, lens, slot, table, 1, n_tok, H, G, z["window"],
+                                           0.088, variant="tc"), iters)
+        else:
+            from .csrc import attention_bf16
+            n = attention_bf16.decode_splits(seqs, G, past + per, z["window"])
+            us = _time(lambda: att.decode(q, kp, vp, om, lens, slot, table, H, G, z["window"], 0.088, n, ws), iters)
+        report("  like: attention (Mistral)", case, us, cache_w + n_tok * H * 128 * 4.0, 4.0 * H * 128 * seen_win)
+        us = _time(lambda: o.diff_heads(maps, 0.3, 1e-5, 0.8, out, H, vdim), iters)
+        report("diff_heads", case, us, n_tok * H * vdim * 6.0, 0.0)
+        gate = torch.randn((n_tok, H * vdim), device=dev)
+        us = _time(lambda: o.sigmoid_gate(out, gate), iters)
+        report("sigmoid_gate", case, us, n_tok * H * vdim * 8.0, 0.0)
+        # --- rotation, unit norm and cache write of both mixers, beside Mistral's rotation + cache write
+        cols_d = (H + G) * wd + G * vdim
+        zd = torch.randn((n_tok, cols_d), device=dev)
+        inv_d = torch.tensor([1e4 ** (-2.0 * i / dd) for i in range(dd // 2)], device=dev)
+        us = _time(lambda: o.rotary_cache_write(zd, inv_d, dd, 0, False, 1e-5, q2, kd, vp, pos, seq, slot, table,
+                                                2 * H, 2 * G, G, dd, vdim, 2), iters)
+        report("rotary_cache_write (two maps)", case, us, n_tok * (cols_d * 6.0 + 2 * H * wd * 2.0), 0.0)
+        cols_w = (H + G) * dim + G * vdim
+        zw = torch.randn((n_tok, cols_w + H * vdim), device=dev)
+        inv_w = torch.tensor([1e4 ** (-4.0 * i / dim) for i in range(dim // 4)], device=dev)
+        us = _time(lambda: o.rotary_cache_write(zw, inv_w, dim // 2, 1, True, 1e-5, q, kp, vp, pos, seq, slot, table,
+                                                H, G, G, dim, vdim, 1), iters)
+        report("rotary_cache_write (unit norm)", case, us, n_tok * cols_w * 6.0, 0.0)
+        qkv = torch.randn((n_tok, (H + 2 * G) * 128), device=dev)
+        inv128 = torch.tensor([1e6 ** (-i / 64.0) for i in range(64)], device=dev)
+        us = _time(lambda: o.rope_cache_write(qkv, q, kp, vp, pos, seq, slot, table, inv128, 0, H, G, 128), iters)
+        report("  like: rope_cache_write", case, us, n_tok * (H + 2 * G) * 128 * 6.0, 0.0)
+        # --- the block's kernel: norm of the sublayer's output, sum into the stream, the next norm
+        x = torch.randn((n_tok, W), device=dev)
+        y = torch.randn((n_tok, W), device=dev)
+        wb = torch.ones(W, device=dev, dtype=bf)
+        xb = torch.empty((n_tok, W), device=dev, dtype=bf)
+        us = _time(lambda: o.norm_add_norm(y, wb, 1e-5, x, wb, 1e-5, xb), iters)
+        report("norm_add_norm", case, us, n_tok * W * 14.0, 0.0)
+        us = _time(lambda: o.rmsnorm(x, wb, 1e-5, xb), iters)
+        report("  like: rmsnorm", case, us, n_tok * W * 6.0, 0.0)
+        # --- dense feed-forward: the up product with the squared relu in its epilogue, beside the SwiGLU
+        # product of equal weight
+        f, lf = z["ff"], z["like_ff"]
+        xn = torch.randn((n_tok, W), device=dev, dtype=bf)
+        copies = max(2, int(400e6 // (f * W * 2)) + 1)      # rotate weights: more than the L2 holds
+        w_up = [torch.randn((f, W), device=dev, dtype=bf) * 0.02 for _ in range(copies)]
+        act = torch.empty((n_tok, f), device=dev, dtype=bf)
+        turn = {"i": 0}
+
+        def up_relu():
+            turn["i"] += 1
+            assert gm.run(xn, w_up[turn["i"] % copies], act, ops.MODE_STORE_ACT, act=(ops.ACT_RELU_SQUARED,))
+        us = _time(up_relu, few)
+        report("gemm_tc (up, relu^2)", case, us, f * W * 2.0 + n_tok * (W + f) * 2.0, 2.0 * n_tok * f * W)
+        zf = torch.empty((n_tok, f), device=dev)
+        us = _time(lambda: o.relu_squared(zf, act), iters)
+        report("  (relu_squared alone, not on the bf16 path)", case, us, n_tok * f * 6.0, 0.0)
+        w_gu = [torch.randn((2 * lf, W), device=dev, dtype=bf) * 0.02 for _ in range(copies)]
+        act_l = torch.empty((n_tok, lf), device=dev, dtype=bf)
+
+        def gate_up():
+            turn["i"] += 1
+            assert gm.run(xn, w_gu[turn["i"] % copies], act_l, ops.MODE_SWIGLU)
+        us = _time(gate_up, few)
+        report("  like: gemm_tc (gate, up, silu)", case, us, 2 * lf * W * 2.0 + n_tok * (W + lf) * 2.0,
+               4.0 * n_tok * lf * W)
+        # --- the shared expert's gate and up product with the clamps in its epilogue
+        ef = z["e_ff"]
+        act_s = torch.empty((n_tok, ef), device=dev, dtype=bf)
+        w_s = [w.view(-1)[:2 * ef * W].view(2 * ef, W) for w in w_up]
+
+        def shared_up():
+            turn["i"] += 1
+            assert gm.run(xn, w_s[turn["i"] % copies], act_s, ops.MODE_SWIGLU, act=(ops.ACT_CLAMPED_GLU, 7.0, 1.702))
+        us = _time(shared_up, few)
+        report("gemm_tc (shared gate, up, clamps)", case, us, 2 * ef * W * 2.0 + n_tok * (W + ef) * 2.0,
+               4.0 * n_tok * ef * W)
+
+        def shared_like():
+            turn["i"] += 1
+            assert gm.run(xn, w_s[turn["i"] % copies], act_s, ops.MODE_SWIGLU)
+        us = _time(shared_like, few)
+        report("  like: gemm_tc (gate, up, silu)", case, us, 2 * ef * W * 2.0 + n_tok * (W + ef) * 2.0,
+               4.0 * n_tok * ef * W)
+        # --- the router: sigmoid scores, the best groups, the choice; beside the softmax router
+        E, top = z["experts"], z["top"]
+        zr = torch.randn((n_tok, E), device=dev)
+        idx = torch.empty((n_tok, top), dtype=torch.int32, device=dev)
+        wt = torch.empty((n_tok, top), device=dev)
+        us = _time(lambda: o.moe_route_grouped(zr, z["groups"], z["keep"], top, 2.5, idx, wt), iters)
+        report("moe_route_grouped", case, us, n_tok * (E * 4.0 + top * 8.0), 0.0)
+        corr = torch.zeros(E, device=dev)
+        us = _time(lambda: o.moe_route(zr, corr, top, idx, wt), iters)
+        report("  like: moe_route (Tovapel)", case, us, n_tok * (E * 4.0 + top * 8.0), 0.0)
+    return rows
+
 def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     from . import from_random
     from .config import config_from_dict
@@ -663,14 +861,15 @@ def timeline(B: int, context: int, layers: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline", "decode",
-                                     "kikopel-kernels", "tovapel-kernels"])
+                                     "kikopel-kernels", "tovapel-kernels", "rupasun-kernels"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     ap.add_argument("--model", default="mistral7b", choices=sorted(MODEL_SIZES),
                     help="step, timeline: whose layer sizes the model has")
     ap.add_argument("--kikopel-size", default="1b", choices=sorted(KIKOPEL_SIZES),
-                    help="kikopel-kernels / tovapel-kernels TOKENS BATCH CONTEXT: whose layer sizes the kernels get")
+                    help="kikopel-kernels / tovapel-kernels / rupasun-kernels TOKENS BATCH CONTEXT: whose layer sizes "
+                         "the kernels get")
     ap.add_argument("--window", type=int, default=0, help="decode: the sliding window (0: none)")
     ap.add_argument("--equal-shares", action="store_true",
                     help="decode: every sequence's keys in equal shares (no page quantum)")
@@ -684,6 +883,9 @@ def main() -> None:
         attention_bf16.decode_splits = lambda *args, **kw: a.splits
     if a.what == "tovapel-kernels":
         tovapel_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
+        return
+    if a.what == "rupasun-kernels":
+        rupasun_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
         return
     if a.what == "kikopel-kernels":
         kikopel_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)

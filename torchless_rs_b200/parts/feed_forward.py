@@ -150,8 +150,10 @@ class ReluSquaredFeedForward:
     def forward(self, xn, residual: torch.Tensor, batch, emit=None, overwrite: bool = False) -> None:
         rt, ws = self.rt, self.rt.workspace
         T = residual.shape[0]
-        z = ws.get("ffn_pre", (T, self.inter), torch.float32)
-        self.matmul(xn, self.w_up, z, ops.MODE_STORE_F32)
         act = ws.get("ffn_act", (T, self.inter), rt.act_dtype)
-        rt.ops.relu_squared(z, act)
+        # the square of the relu in the product's epilogue, on the 32-bit sums, where the kernel has one
+        if not self.matmul.activated(xn, self.w_up, act, ops.MODE_STORE_ACT, (ops.ACT_RELU_SQUARED,)):
+            z = ws.get("ffn_pre", (T, self.inter), torch.float32)
+            self.matmul(xn, self.w_up, z, ops.MODE_STORE_F32)
+            rt.ops.relu_squared(z, act)
         self.matmul(act, self.w_down, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)

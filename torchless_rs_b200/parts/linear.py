@@ -56,3 +56,9 @@ class Matmul:
             return self.fast.rope_applied
         self.rt.ops.gemm_generic(a, w, out, mode)
         return False
+
+    def activated(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, act) -> bool:
+        """The product with another activation in its epilogue than the mode's own (`act` as
+        `GemmBf16.run` takes it): True if the tensor-core kernel took it, False if the caller has to
+        run the product into 32-bit and the activation as a kernel of its own."""
+        return self.fast is not None and self.fast.run(a, w, out, mode, act=act)

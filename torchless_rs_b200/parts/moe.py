@@ -166,8 +166,10 @@ class GroupedSigmoidMoE:
         rt.ops.moe_gemm(act, None, self.w_down, yk, offsets, up=False)
         rt.ops.moe_combine(yk, row_of, wt, xn, residual, accumulate=not overwrite)
         if self.shared_ff:
-            zs = ws.get("moe_shared_pre", (T, 2 * self.shared_ff), torch.float32)
-            self.matmul(xn, self.w_shared_up, zs, ops.MODE_STORE_F32)
             sact = ws.get("moe_shared_act", (T, self.shared_ff), rt.act_dtype)
-            rt.ops.clamped_glu(zs, self.shared_limit, self.gate_alpha, sact)
+            if not self.matmul.activated(xn, self.w_shared_up, sact, ops.MODE_SWIGLU,
+                                         (ops.ACT_CLAMPED_GLU, self.shared_limit, self.gate_alpha)):
+                zs = ws.get("moe_shared_pre", (T, 2 * self.shared_ff), torch.float32)
+                self.matmul(xn, self.w_shared_up, zs, ops.MODE_STORE_F32)
+                rt.ops.clamped_glu(zs, self.shared_limit, self.gate_alpha, sact)
             self.matmul(sact, self.w_shared_down, residual, ops.MODE_ACCUM_F32)
