@@ -89,6 +89,13 @@ CONFIGS = {
         layer(window_mixer(2, 2, 128, 128, window=None, rot=64, softcap=10.0), dense(256)),
         layer(diff_mixer(2, 1, 64, 32, diff=0.7, rot=16, base=300.0), None),
     ]),
+    # two maps together as wide as the values (64 and 128), a window without a cap: what the plain attention
+    # kernels take in bfloat16
+    "S": config(128, 300, [
+        layer(diff_mixer(2, 1, 64, 128, diff=0.4, rot=64), dense(192)),
+        layer(window_mixer(4, 2, 64, 64, window=70, rot=32), None),
+        layer(diff_mixer(4, 2, 32, 64, diff=0.6, rot=16, base=900.0), moe(32, experts=4, top=2, groups=2, keep=1, scale=1.5)),
+    ]),
 }
 
 

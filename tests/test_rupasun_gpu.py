@@ -17,7 +17,7 @@ from rupasun_tiny import CONFIGS, TModel, make_weights, sure_tokens, tokens_of, 
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-BOTH = [(c, d) for c in ("P", "Q", "R") for d in ("float32", "bfloat16")]
+BOTH = [(c, d) for c in ("P", "Q", "R") for d in ("float32", "bfloat16")] + [("S", "bfloat16")]
 
 
 def assert_close(got, ref, dtype, what=""):
@@ -98,7 +98,7 @@ def test_unequal_batches_equal_each_request_alone(name, dtype):
     tm.engine.cache.check()
 
 
-@pytest.mark.parametrize("name,dtype", [("P", "float32"), ("R", "bfloat16"), ("Q", "float32")])
+@pytest.mark.parametrize("name,dtype", [("P", "float32"), ("R", "bfloat16"), ("Q", "float32"), ("S", "bfloat16")])
 def test_slots_and_pages_are_clean_when_used_again(name, dtype):
     """A cache that holds one request at a time: every request gets the slot and the pages that the one
     before left behind, keys of the longer request still in them."""
@@ -284,13 +284,13 @@ def _split(z, H, G, dim, vdim, slots):
 def test_projections_are_rotated_normed_and_written_to_their_pages(dtype, H, G, dim, vdim, rot, slots, style, unit):
     """Both pairings, rotation of a part and of nothing, with and without the unit norm, one and two maps
     per head: q, and k and v where the pages hold them; positions up to some thousands (32-bit angles),
-    a step that crosses a page border; pages of other sequences stay untouched."""
+    a step that crosses a page border, steps of few and of many tokens; pages of other sequences stay
+    untouched."""
     o = _ops(dtype)
     rng = np.random.default_rng(dim + rot)
     base, eps = 5000.0, 1e-5
     cols = (H + G) * slots * dim + G * vdim
-    for first in (0, 60, 3000):
-        T = 70
+    for first, T in ((0, 70), (60, 70), (3000, 70), (37, 300), (1000, 257)):      # few tokens; many (another kernel)
         pos = np.arange(first, first + T)
         pages = _Pages(dtype, first + T, G, slots * dim, vdim)
         z = rng.normal(0, 1.0, (T, cols + 3)).astype(np.float32)        # further columns follow and are not read
@@ -607,12 +607,33 @@ def test_activations_of_the_feed_forwards(dtype):
         u = np.clip(z[:, 5 + n:].astype(np.float64), -limit, limit)
         ref = g * plain.sigmoid(1.702 * g) * (u + 1.0)
         assert np.abs(out.float().cpu().numpy() - ref).max() <= max(tol, 2e-6) * np.abs(ref).max()
-    x = torch.as_tensor(rng.normal(0, 1.0, (T, n)), dtype=dtype)
-    gate = rng.normal(0, 3.0, (T, n + 4)).astype(np.float32)
-    xd = x.cuda()
-    o.sigmoid_gate(xd, _dev(gate)[:, 4:])
-    ref = x.double().numpy() * plain.sigmoid(gate[:, 4:].astype(np.float64))
-    assert np.abs(xd.float().cpu().numpy() - ref).max() <= max(tol, 2e-6) * np.abs(ref).max()
+    for m, skip in ((n, 4), (n, 3), (52, 8), (256, 4)):        # rows that are and are not taken four entries at a time
+        x = torch.as_tensor(rng.normal(0, 1.0, (T, m)), dtype=dtype)
+        gate = rng.normal(0, 3.0, (T, m + skip)).astype(np.float32)
+        xd = x.cuda()
+        o.sigmoid_gate(xd, _dev(gate)[:, skip:])
+        ref = x.double().numpy() * plain.sigmoid(gate[:, skip:].astype(np.float64))
+        assert np.abs(xd.float().cpu().numpy() - ref).max() <= max(tol, 2e-6) * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,vdim", [(3, 7), (2, 24), (5, 128), (1, 132), (2, 512), (1, 260)])
+def test_difference_of_maps_is_normed_per_head(dtype, H, vdim):
+    """o = a1 - lambda a2, o / rms(o) * mult per head, for value sizes that are and are not taken four at a time;
+    one head's maps nearly cancel (the norm then lifts what is left)."""
+    o = _ops(dtype)
+    rng = np.random.default_rng(H * vdim)
+    T, lam, eps, mult = 19, 0.6, 1e-5, 0.7
+    a = rng.normal(0, 1.0, (T, H, 2, vdim))
+    a[3, 0, 0] = lam * a[3, 0, 1] + 1e-2 * rng.normal(0, 1.0, vdim)
+    ad = torch.as_tensor(a, dtype=torch.float32).to(dtype)
+    a64 = ad.double().numpy()
+    d = a64[:, :, 0] - lam * a64[:, :, 1]
+    ref = plain.rms_normalise(d, eps) * mult
+    out = torch.zeros((T, H * vdim), dtype=dtype).cuda()
+    o.diff_heads(ad.reshape(T, -1).cuda(), lam, eps, mult, out, H, vdim)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert np.abs(out.float().cpu().numpy().reshape(T, H, vdim) - ref).max() <= tol * np.abs(ref).max()
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 256, 512), (8, 1408, 2048), (40, 384, 4096), (100, 512, 1024), (130, 640, 512),

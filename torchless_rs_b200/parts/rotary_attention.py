@@ -17,7 +17,9 @@ twice the size and read every key and every value once per group.
 
 Both: one stacked product for the projections of the input (32-bit), one kernel that rotates, norms
 and writes q and the token's k and v into the pages, attention from pages only (so a position's
-result does not depend on the step that computes it), a closing kernel, W_o."""
+result does not depend on the step that computes it), a closing kernel, W_o.  Attention runs on the
+kernels of the plain rotary attention where these take it (bfloat16, no cap, a key row as wide as a
+value row, 32, 64 or 128), else on those of the windowed attention with a cap."""
 from __future__ import annotations
 
 from typing import Dict
@@ -61,6 +63,13 @@ class _RotaryAttention:
         self.rt = rt
         self.matmul = Matmul(rt)
         self.cache = None
+        # scores without a cap over keys and values of one size are what the framework's plain
+        # attention kernels compute (tensor-memory kernels for prompts, split keys for decode steps)
+        self.fast = None
+        if not rt.is_f32 and self.width == self.vdim:
+            from ..csrc import attention_bf16
+            if self.width in attention_bf16.FAST_HEAD_DIMS:
+                self.fast = attention_bf16.AttentionBf16.get(self.width)
 
     @property
     def width(self) -> int:
@@ -91,6 +100,10 @@ class _RotaryAttention:
 
     def _attend(self, q, out, batch, softcap):
         c = self.cache
+        if self.fast is not None and softcap is None and \
+                self.fast.run(q, c, out, batch, self.nh * self.slots, self.nkv, self.window, self.scale,
+                              self.rt.workspace):
+            return
         run_attention(self.rt.ops, q, c.k_pages, c.v_pages, None, None, out, batch.token_pos, batch.token_seq,
                       batch.seq_slot, c.page_table, self.nh * self.slots, self.nkv, self.width, self.vdim,
                       self.window, 0, self.scale, softcap, batch, self.rt.workspace)
