@@ -664,3 +664,80 @@ def test_products_apply_the_activations_in_their_epilogues(M, N, K):
     ref = z[:, :N] * plain.sigmoid(z[:, :N]) * z[:, N:]
     assert np.abs(out.float().cpu().numpy() - ref).max() <= 1e-2 * np.abs(ref).max()
     assert gm.take_error() == 0
+
+
+class _Step:
+    """What the attention kernels read of a step: one sequence's tokens first..last."""
+
+    def __init__(self, pages, first, last):
+        self.n_seqs, self.is_decode, self.max_new = 1, False, last - first + 1
+        self.seq_start, self.seq_len, self.seq_slot = _i32([0, last - first + 1]), _i32([last + 1]), _i32([pages.slot])
+
+
+class _View:
+    def __init__(self, pages):
+        self.k_pages, self.v_pages, self.page_table = pages.k, pages.v, _i32(pages.table)
+
+
+@pytest.mark.parametrize("H,G,dim,rot,window,cap", [(4, 2, 64, 32, 70, 8.0), (2, 1, 128, 64, 130, 30.0), (4, 4, 64, 64, None, 9.0),
+                                                   (2, 2, 128, 128, 64, None), (8, 1, 64, 0, 1, 20.0)])
+def test_tensor_memory_attention_takes_caps_and_windows(H, G, dim, rot, window, cap):
+    """Prompt steps of at least 128 tokens on the kernels of the plain attention (keys as wide as values, 64
+    or 128), with and without a cap: every row of a whole prompt and of a portion that continues a held
+    sequence against the plain softmax.  One key scores 16 where the others score around 1.6 and has a value
+    of its own, on and beside page borders: the rows up to `window - 1` after it return that value, the next
+    one does not, and the cap (below 16) decides how much of it."""
+    from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
+    dtype, vdim = torch.bfloat16, dim
+    o = _ops(dtype)
+    fast = AttentionBf16.get(dim)
+    rng = np.random.default_rng(dim + (window or 0))
+    base, eps = 1e7, 1e-6
+    n = 5 * 64 + 9
+    mark = (rot - 2) if rot else 0
+    scale = 16.0 / (3.0 / np.sqrt((9.0 + (dim - 1) * 0.09) / dim) * np.sqrt(dim))
+    pos_all = np.arange(n)
+    for target in (63, 64, 3 * 64 - 1, 130):
+        zq = rng.normal(0, 0.3, (n, H, dim))
+        zk = rng.normal(0, 0.3, (n, G, dim))
+        zv = rng.normal(0, 0.3, (n, G, vdim))
+        zk[:, :, mark] = 0.0
+        zk[target] = 0.0
+        zk[target, :, mark] = 4.0
+        zv[target, :, 0] = 50.0
+        zq[:, :, mark] = 3.0
+        z = _join(zq, zk, zv)
+        pages = _Pages(dtype, n, G, dim, vdim)
+        q = _write(o, pages, z, pos_all, rot, base, 1, True, eps, H, G, dim, vdim, 1, dtype)
+        zq, zk, zv = _split(z.astype(np.float64), H, G, dim, vdim, 1)
+        p64 = pos_all.astype(np.float64)
+        qr = plain.rms_normalise(plain.rotate(zq, p64, rot, base, True), eps)
+        kr = plain.rms_normalise(plain.rotate(zk, p64, rot, base, True), eps)
+        vis = plain.visible(p64, window)
+        ref = np.zeros((n, H, vdim))
+        for h in range(H):
+            g = h // (H // G)
+            s = (qr[:, h] @ kr[:, g].T) * scale
+            if cap:
+                s = cap * np.tanh(s / cap)
+            ref[:, h] = plain.softmax_rows(s, vis) @ zv[:, g]
+        last_seen = n - 1 if window is None else min(n - 1, target + window - 1)
+        assert (np.abs(ref[last_seen, :, 0]) > 5.0).all(), "the test's own mark does not stand out"
+        if last_seen + 1 < n:
+            assert (np.abs(ref[last_seen + 1, :, 0]) < 2.0).all(), "the mark is seen outside the window"
+        for first, last in ((0, n - 1), (n - 200, n - 1), (target + 1, target + 128), (0, 127)):
+            if last >= n:
+                continue
+            out = torch.zeros((last - first + 1, H * vdim), dtype=dtype).cuda()
+            step, view = _Step(pages, first, last), _View(pages)
+            qs = q[first:last + 1].contiguous()
+            if cap:
+                assert fast.run_capped(qs, view, out, step, H, G, window, scale, cap), "the kernel did not take the step"
+            else:
+                fast.prefill(qs, view.k_pages, view.v_pages, out, step.seq_start, step.seq_len, step.seq_slot,
+                             view.page_table, 1, step.max_new, H, G, window, scale, variant="tc")
+            got = out.float().cpu().numpy().reshape(-1, H, vdim)
+            err = np.abs(got - ref[first:last + 1])
+            assert err.max() <= 2.5e-2 * max(1.0, np.abs(ref).max()), \
+                f"target {target} rows {first}..{last}: {err.max():.3e} at row {first + int(err.max(axis=(1, 2)).argmax())}"
+        assert fast.take_error() == 0

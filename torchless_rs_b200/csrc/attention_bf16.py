@@ -135,6 +135,8 @@ class AttentionBf16:
                 self._prefill_tma.restype = c_int
                 self._prefill_tc = getattr(self.lib, f"tl_attn_prefill_tc_hd{head_dim}")
                 self._prefill_tc.restype = c_int
+                self._prefill_tc_cap = getattr(self.lib, f"tl_attn_prefill_tc_cap_hd{head_dim}")
+                self._prefill_tc_cap.restype = c_int
                 self._tc_error = getattr(self.lib, f"tl_attn_tc_take_error_hd{head_dim}")
                 self._tc_error.restype = c_int
                 self._tma_error = getattr(self.lib, f"tl_attn_tma_take_error_hd{head_dim}")
@@ -222,6 +224,26 @@ class AttentionBf16:
                              c_int(page_table.stride(0)), c_int(n_seqs), c_int(max_new), c_int(nh),
                              c_int(nkv), c_int(window or 0), c_float(scale), _stream()),
                "attn_prefill")
+
+    def run_capped(self, q, cache_view, out, batch, nh, nkv, window, scale, cap) -> bool:
+        """A prompt step whose scores are capped, s <- cap tanh(s scale / cap), on the tensor-memory kernel.
+        False where that kernel does not take the step (decode steps, few new tokens, other head sizes):
+        the caller then uses a kernel that does."""
+        if getattr(self, "_prefill_tc_cap", None) is None or nh // nkv > MAX_GROUP or batch.is_decode or \
+                batch.max_new < 128:
+            return False
+        c = cache_view
+        for t, n in ((q, "q"), (c.k_pages, "k pages"), (c.v_pages, "v pages"), (out, "out")):
+            _need(t, torch.bfloat16, f"attn prefill {n}")
+        st = self._prefill_tc_cap(_ptr(q), c_longlong(q.shape[0]), _ptr(c.k_pages), _ptr(c.v_pages),
+                                  c_longlong(c.k_pages.shape[0]), _ptr(out), _ptr(batch.seq_start),
+                                  _ptr(batch.seq_len), _ptr(batch.seq_slot), _ptr(c.page_table),
+                                  c_int(c.page_table.stride(0)), c_int(batch.n_seqs), c_int(batch.max_new), c_int(nh),
+                                  c_int(nkv), c_int(window or 0), c_float(scale), c_float(cap), _stream())
+        if st == -2:
+            return False
+        _check(st, "attn_prefill_tc_cap")
+        return True
 
     def run(self, q, cache_view, out, batch, nh, nkv, window, scale, workspace) -> bool:
         if self.lib is None or nh // nkv > MAX_GROUP:

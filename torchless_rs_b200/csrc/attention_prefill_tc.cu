@@ -187,12 +187,18 @@ __device__ __forceinline__ uint32_t tc_idesc(int n) {   // bf16 x bf16 -> f32, M
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// CAP: the scaled scores are capped, s <- cap tanh(s scale / cap), before mask and softmax; `scale_log2` is
+// then log2(e) alone, `cap_c2` = 2 log2(e) scale / cap, and tanh(x) = 1 - 2 / (e^(2x) + 1) by one fast
+// exponential and one fast reciprocal (absolute error about 1e-7; exact at both ends: 2^x overflows to
+// infinity, whose reciprocal is 0, and underflows to 0).
+template <bool CAP>
 __global__ void __launch_bounds__(TC_THREADS)
 FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, __nv_bfloat16* __restrict__ out,
                            const int* __restrict__ seq_start, const int* __restrict__ seq_len,
                            const int* __restrict__ seq_slot, const int* __restrict__ page_table,
-                           int table_stride, int nh, int nkv, int window, float scale_log2) {
+                           int table_stride, int nh, int nkv, int window, float scale_log2, float cap,
+                           float cap_c2) {
   // The tiles need 1024-byte alignment (128-byte swizzle) and two blocks per SM leave no room
   // for padding, so the dynamic shared memory itself must start on such a boundary (it does
   // when the kernel has no static shared memory; checked below).
@@ -356,6 +362,17 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
       tc_ld32(t_s + (uint32_t)(i & 1) * PAGE + 32, sb);
       tc_wait_ld();
       const int key0 = (ps + i) * PAGE;
+      if (CAP) {
+        const float m2cap = -2.0f * cap;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float ra, rb;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(tc_ex2(__uint_as_float(sa[j]) * cap_c2) + 1.0f));
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rb) : "f"(tc_ex2(__uint_as_float(sb[j]) * cap_c2) + 1.0f));
+          sa[j] = __float_as_uint(fmaf(m2cap, ra, cap));
+          sb[j] = __float_as_uint(fmaf(m2cap, rb, cap));
+        }
+      }
       // a page that every row of this warp sees whole needs no mask (all but the pages on the
       // diagonal and at a window's edge)
       const bool whole = __all_sync(0xffffffffu, valid_row && key0 >= lo && key0 + PAGE - 1 <= pos);
@@ -510,11 +527,12 @@ static bool tc_make_map(CUtensorMap* map, const void* ptr, long long rows, long 
 
 // q, out [T, nh*HEAD_DIM]; max_new = the most new tokens any sequence of the step has.
 // Returns -2 for sizes this kernel does not take.
-extern "C" int FN(tl_attn_prefill_tc)(const void* q, long long T, const void* k_pages, const void* v_pages,
-                                      long long n_pages, void* out, const int* seq_start,
-                                      const int* seq_len, const int* seq_slot, const int* page_table,
-                                      int table_stride, int B, int max_new, int nh, int nkv, int window,
-                                      float scale, cudaStream_t stream) {
+// `cap` > 0: scores are capped, s <- cap tanh(s scale / cap).
+extern "C" int FN(tl_attn_prefill_tc_cap)(const void* q, long long T, const void* k_pages, const void* v_pages,
+                                          long long n_pages, void* out, const int* seq_start,
+                                          const int* seq_len, const int* seq_slot, const int* page_table,
+                                          int table_stride, int B, int max_new, int nh, int nkv, int window,
+                                          float scale, float cap, cudaStream_t stream) {
 #if HEAD_DIM % 64 != 0
   return -2;
 #else
@@ -529,18 +547,34 @@ extern "C" int FN(tl_attn_prefill_tc)(const void* q, long long T, const void* k_
   const size_t smem = TC_SMEM_BYTES;   // the last 256 bytes hold the barriers
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(FN(attn_prefill_tc_kernel),
+    cudaError_t e = cudaFuncSetAttribute(FN(attn_prefill_tc_kernel)<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(FN(attn_prefill_tc_kernel)<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int q_tiles = (max_new + TC_Q - 1) / TC_Q;
   if (q_tiles > 65535) return -2;
   dim3 grid(nh, q_tiles, B);
-  return tl_launch(FN(attn_prefill_tc_kernel), grid, dim3(TC_THREADS), smem, stream, tq, tk, tv,
+  const float log2e = 1.4426950408889634f;
+  if (cap > 0.0f)
+    return tl_launch(FN(attn_prefill_tc_kernel)<true>, grid, dim3(TC_THREADS), smem, stream, tq, tk, tv,
+                     (__nv_bfloat16*)out, seq_start, seq_len, seq_slot, page_table, table_stride, nh, nkv,
+                     window, log2e, cap, 2.0f * log2e * scale / cap);
+  return tl_launch(FN(attn_prefill_tc_kernel)<false>, grid, dim3(TC_THREADS), smem, stream, tq, tk, tv,
                    (__nv_bfloat16*)out, seq_start, seq_len, seq_slot, page_table, table_stride, nh, nkv,
-                   window, scale * 1.4426950408889634f);
+                   window, scale * log2e, 0.0f, 0.0f);
 #endif
+}
+
+extern "C" int FN(tl_attn_prefill_tc)(const void* q, long long T, const void* k_pages, const void* v_pages,
+                                      long long n_pages, void* out, const int* seq_start,
+                                      const int* seq_len, const int* seq_slot, const int* page_table,
+                                      int table_stride, int B, int max_new, int nh, int nkv, int window,
+                                      float scale, cudaStream_t stream) {
+  return FN(tl_attn_prefill_tc_cap)(q, T, k_pages, v_pages, n_pages, out, seq_start, seq_len, seq_slot, page_table,
+                                    table_stride, B, max_new, nh, nkv, window, scale, 0.0f, stream);
 }
 
 extern "C" int FN(tl_attn_tc_take_error)() {

@@ -138,7 +138,9 @@ __device__ __forceinline__ void ra_store4(__nv_bfloat16* p, const float (&v)[4])
 //    already on its way from memory while it works on this one;
 //  - the blocks after them: 32 consecutive tokens of one value head each; the tile is turned in
 //    shared memory, so that the transposed value pages are written in runs of positions.
+// R: 32-entry pieces of a vector per lane (dim <= 32 R).
 #define RAM_WARPS 8
+template <int R>
 __global__ void __launch_bounds__(RAM_WARPS * 32)
 rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ inv_freq, int rot,
                                int style, int unit_norm, float eps, act_t* __restrict__ q_out,
@@ -189,7 +191,6 @@ rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float
     cs[i] = make_float2(c, sn);
   }
   __syncthreads();
-  constexpr int R = RA_MAX_DIM / 32;
   float cur[R], nxt[R];
   int j = warp;
   if (j < nq + nk) {
@@ -280,9 +281,15 @@ extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const flo
   const size_t smem = tile_bytes > token_bytes ? tile_bytes : token_bytes;
   if (T >= 256 && smem <= 48 * 1024) {
     const unsigned blocks = (unsigned)T + (unsigned)((T + 31) / 32) * (unsigned)nv;
-    return tl_launch(rotary_cache_write_many_kernel, dim3(blocks), dim3(RAM_WARPS * 32), smem, stream, z, ldz, inv_freq,
-                     rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, token_pos, token_seq,
-                     seq_slot, page_table, table_stride, T, nq, nk, nv, dim, vdim, slots);
+#define RA_MANY(R_)                                                                                                  \
+    return tl_launch(rotary_cache_write_many_kernel<R_>, dim3(blocks), dim3(RAM_WARPS * 32), smem, stream, z, ldz,  \
+                     inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages,         \
+                     token_pos, token_seq, seq_slot, page_table, table_stride, T, nq, nk, nv, dim, vdim, slots)
+    if (dim <= 32) RA_MANY(1);
+    if (dim <= 64) RA_MANY(2);
+    if (dim <= 128) RA_MANY(4);
+    RA_MANY(8);
+#undef RA_MANY
   }
   const dim3 grid(T, (vectors + RA_WARPS - 1) / RA_WARPS);
   return tl_launch(rotary_cache_write_kernel, grid, dim3(RA_WARPS * 32), 0, stream, z, ldz, inv_freq, rot, style,
@@ -321,6 +328,7 @@ diff_heads_kernel(const act_t* __restrict__ a, float lambda, float eps, float mu
 }
 
 // The same with four values per lane at a time (value sizes that are multiples of 4, up to 512).
+template <int N>     // 128-entry pieces of a head's values per warp (vdim <= 128 N)
 __global__ void __launch_bounds__(256)
 diff_heads_vec_kernel(const act_t* __restrict__ a, float lambda, float eps, float mult, act_t* __restrict__ out,
                       int rows, int vdim) {
@@ -331,10 +339,10 @@ diff_heads_vec_kernel(const act_t* __restrict__ a, float lambda, float eps, floa
   if (r >= rows) return;
   const act_t* a1 = a + (size_t)r * 2 * vdim;
   const act_t* a2 = a1 + vdim;
-  float o[4][4];
+  float o[N][4];
   float ss = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < N; ++i) {
     const int d = (lane + 32 * i) * 4;
     float x[4] = {0.0f, 0.0f, 0.0f, 0.0f}, y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (d < vdim) { ra_load4(a1 + d, x); ra_load4(a2 + d, y); }
@@ -347,7 +355,7 @@ diff_heads_vec_kernel(const act_t* __restrict__ a, float lambda, float eps, floa
   ss = warp_sum(ss);
   const float f = mult / sqrtf(ss / (float)vdim + eps);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < N; ++i) {
     const int d = (lane + 32 * i) * 4;
     if (d < vdim) {
       float w[4];
@@ -364,9 +372,15 @@ extern "C" int TL_NAME(tl_diff_heads)(const void* a, float lambda, float eps, fl
   if (heads < 1 || vdim < 1) return TL_ERR_BAD_ARG;
   if (vdim > 32 * DH_MAX_PER_LANE) return TL_ERR_UNSUPPORTED;
   const long long rows = (long long)T * heads;
-  if (vdim % 4 == 0 && vdim <= 512 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)out & 15) == 0)
-    return tl_launch(diff_heads_vec_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, stream, (const act_t*)a,
-                     lambda, eps, mult, (act_t*)out, (int)rows, vdim);
+  if (vdim % 4 == 0 && vdim <= 512 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+#define DH_VEC(N_)                                                                                                \
+    return tl_launch(diff_heads_vec_kernel<N_>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, stream,          \
+                     (const act_t*)a, lambda, eps, mult, (act_t*)out, (int)rows, vdim)
+    if (vdim <= 128) DH_VEC(1);
+    if (vdim <= 256) DH_VEC(2);
+    DH_VEC(4);
+#undef DH_VEC
+  }
   return tl_launch(diff_heads_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, stream, (const act_t*)a,
                    lambda, eps, mult, (act_t*)out, (int)rows, vdim);
 }

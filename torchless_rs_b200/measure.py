@@ -585,20 +585,34 @@ def rupasun_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
 
         class _B:      # what the kernel choice reads of a step
             n_tokens, n_seqs, is_decode, max_len, seq_start, seq_len, seq_slot = n_tok, seqs, per == 1, past + per, start, lens, slot
+            max_new, len_bucket = per, past + per
+
+        class _C:      # the cache view of the attention kernels
+            pass
+
+        def attend(qq, kk, vv, oo, heads, width, window, scale, cap):
+            """The mixers' choice of kernel: those of the plain attention where they take the step."""
+            view = _C()
+            view.k_pages, view.v_pages, view.page_table = kk, vv, table
+            fast = AttentionBf16.get(width) if width == vdim and width in (32, 64, 128) else None
+            if fast is not None and cap is None and fast.run(qq, view, oo, _B, heads, G, window, scale, ws):
+                return
+            if fast is not None and cap is not None and fast.run_capped(qq, view, oo, _B, heads, G, window, scale, cap):
+                return
+            run_attention(o, qq, kk, vv, None, None, oo, pos, seq, slot, table, heads, G, width, vdim, window, 0, scale,
+                          cap, _B, ws)
         # --- differential attention: 2 H query rows of two maps' width over G key rows; then the difference
         wd = 2 * dd
         kd = kp if wd == 128 else _paged(seqs, past + per, G, wd)[0]
         q2 = torch.randn((n_tok, 2 * H * wd), device=dev, dtype=bf)
         maps = torch.empty((n_tok, 2 * H * vdim), device=dev, dtype=bf)
-        us = _time(lambda: run_attention(o, q2, kd, vp, None, None, maps, pos, seq, slot, table, 2 * H, G, wd, vdim,
-                                         None, 0, dd ** -0.5, None, _B, ws), few)
+        us = _time(lambda: attend(q2, kd, vp, maps, 2 * H, wd, None, dd ** -0.5, None), few)
         cache_d = 2.0 * seqs * (past + per) * G * (wd + vdim)
         report("attention (two maps)", case, us, cache_d + n_tok * 2 * H * (wd + vdim) * 2.0,
                2.0 * 2 * H * (dd + vdim) * seen_all)
         q = torch.randn((n_tok, H * dim), device=dev, dtype=bf)
         out = torch.empty((n_tok, H * vdim), device=dev, dtype=bf)
-        us = _time(lambda: run_attention(o, q, kp, vp, None, None, out, pos, seq, slot, table, H, G, dim, vdim,
-                                         z["window"], 0, 1.0, 50.0, _B, ws), few)
+        us = _time(lambda: attend(q, kp, vp, out, H, dim, z["window"], 1.0, 50.0), few)
         cache_w = 2.0 * seqs * min(past + per, z["window"]) * G * (dim + vdim)
         report("attention (window, cap)", case, us, cache_w + n_tok * H * (dim + vdim) * 2.0,
                2.0 * H * (dim + vdim) * seen_win)

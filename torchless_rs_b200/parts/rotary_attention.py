@@ -18,8 +18,9 @@ twice the size and read every key and every value once per group.
 Both: one stacked product for the projections of the input (32-bit), one kernel that rotates, norms
 and writes q and the token's k and v into the pages, attention from pages only (so a position's
 result does not depend on the step that computes it), a closing kernel, W_o.  Attention runs on the
-kernels of the plain rotary attention where these take it (bfloat16, no cap, a key row as wide as a
-value row, 32, 64 or 128), else on those of the windowed attention with a cap."""
+kernels of the plain rotary attention where these take it (bfloat16, a key row as wide as a value row,
+32, 64 or 128; with a cap only prompt steps and rows of 64 or 128), else on those of the windowed
+attention with a cap."""
 from __future__ import annotations
 
 from typing import Dict
@@ -100,10 +101,13 @@ class _RotaryAttention:
 
     def _attend(self, q, out, batch, softcap):
         c = self.cache
-        if self.fast is not None and softcap is None and \
-                self.fast.run(q, c, out, batch, self.nh * self.slots, self.nkv, self.window, self.scale,
-                              self.rt.workspace):
-            return
+        if self.fast is not None:
+            H = self.nh * self.slots
+            if softcap is None:
+                if self.fast.run(q, c, out, batch, H, self.nkv, self.window, self.scale, self.rt.workspace):
+                    return
+            elif self.fast.run_capped(q, c, out, batch, H, self.nkv, self.window, self.scale, softcap):
+                return
         run_attention(self.rt.ops, q, c.k_pages, c.v_pages, None, None, out, batch.token_pos, batch.token_seq,
                       batch.seq_slot, c.page_table, self.nh * self.slots, self.nkv, self.width, self.vdim,
                       self.window, 0, self.scale, softcap, batch, self.rt.workspace)
