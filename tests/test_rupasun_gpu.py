@@ -280,7 +280,8 @@ def _split(z, H, G, dim, vdim, slots):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dim,vdim,rot,slots,style,unit", [
     (3, 1, 20, 7, 8, 1, 1, True), (2, 2, 16, 24, 16, 2, 0, False), (4, 2, 64, 32, 32, 1, 0, True),
-    (1, 1, 24, 10, 0, 2, 0, False), (4, 4, 48, 112, 48, 2, 1, False), (2, 1, 128, 64, 128, 1, 1, True)])
+    (1, 1, 24, 10, 0, 2, 0, False), (4, 4, 48, 112, 48, 2, 1, False), (2, 1, 128, 64, 128, 1, 1, True),
+    (2, 1, 64, 16, 24, 1, 1, True), (2, 2, 32, 8, 12, 2, 0, False), (3, 1, 128, 40, 64, 1, 0, True), (5, 5, 16, 16, 8, 2, 1, True)])
 def test_projections_are_rotated_normed_and_written_to_their_pages(dtype, H, G, dim, vdim, rot, slots, style, unit):
     """Both pairings, rotation of a part and of nothing, with and without the unit norm, one and two maps
     per head: q, and k and v where the pages hold them; positions up to some thousands (32-bit angles),

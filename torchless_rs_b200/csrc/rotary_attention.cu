@@ -265,6 +265,117 @@ rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float
   }
 }
 
+// The many-token kernel for vectors of 16, 32, 64 or 128 entries: a lane holds four neighbouring entries
+// (16-byte loads, 8- or 16-byte stores), LPV lanes a vector, so a warp works on 32 / LPV vectors at a
+// time.  The partner of a rotation lies in the same lane (pairs (2i, 2i + 1)) or rot/8 lanes away
+// (pairs (i, i + rot/2); rot a multiple of 8), so nothing is staged in shared memory but the sines.
+template <int LPV>
+__global__ void __launch_bounds__(RAM_WARPS * 32)
+rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ inv_freq, int rot,
+                              int style, int unit_norm, float eps, act_t* __restrict__ q_out,
+                              act_t* __restrict__ k_pages, act_t* __restrict__ v_pages,
+                              const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                              const int* __restrict__ seq_slot, const int* __restrict__ page_table,
+                              int table_stride, int T, int nq, int nk, int nv, int vdim, int slots) {
+  extern __shared__ float ra_sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int dim = 4 * LPV, VPW = 32 / LPV;
+  if ((int)blockIdx.x >= T) {
+    // ---- a tile of values: [32 tokens][vdim + 1] in shared memory
+    const int tile = blockIdx.x - T;
+    const int t0 = (tile / nv) * 32, g = tile % nv;
+    const int nt = min(32, T - t0);
+    const float* src = z + (size_t)(nq + nk) * dim + (size_t)g * vdim;
+    for (int idx = threadIdx.x; idx < nt * vdim; idx += blockDim.x) {
+      const int tt = idx / vdim, d = idx - tt * vdim;
+      ra_sm[tt * (vdim + 1) + d] = src[(size_t)(t0 + tt) * ldz + d];
+    }
+    __syncthreads();
+    if (lane < nt) {
+      const int t = t0 + lane;
+      const int pos = token_pos[t];
+      const int page = page_table[(size_t)seq_slot[token_seq[t]] * table_stride + pos / TL_PAGE];
+      act_t* dst = v_pages + ((size_t)page * nv + g) * vdim * TL_PAGE + (pos % TL_PAGE);
+      for (int d = warp; d < vdim; d += RAM_WARPS) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(ra_sm[lane * (vdim + 1) + d]);
+    }
+    return;
+  }
+  const int t = blockIdx.x;
+  const int pos = token_pos[t];
+  const float* row = z + (size_t)t * ldz;
+  const int half = rot / 2;
+  const int total = nq + nk;
+  const int sub = lane / LPV, l = lane % LPV, d0 = 4 * l;
+  // the first vectors are on their way while the sines are computed
+  int j = warp * VPW + sub;
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (j < total) ra_load4(row + (size_t)j * dim + d0, v);
+  float2* cs = reinterpret_cast<float2*>(ra_sm);            // [half] (cosine, sine)
+  const float fpos = (float)pos;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, c;
+    sincosf(fpos * inv_freq[i], &sn, &c);
+    cs[i] = make_float2(c, sn);
+  }
+  const int slot = seq_slot[token_seq[t]];
+  const int page = page_table[(size_t)slot * table_stride + pos / TL_PAGE];
+  const int in_page = pos % TL_PAGE;
+  const int width = slots * dim;
+  const int nkv = nk / slots;
+  const int hl = half >> 2;                                  // lanes between the partners (pairs (i, i + half))
+  const int partner = (lane - l) + (l < hl ? l + hl : (l < 2 * hl ? l - hl : l));
+  __syncthreads();
+  for (int j0 = warp * VPW; j0 < total; j0 += RAM_WARPS * VPW) {
+    j = j0 + sub;
+    const int jn = j + RAM_WARPS * VPW;
+    if (jn < total) ra_load4(row + (size_t)jn * dim + d0, nx);
+    float o[4];
+    if (style == 0) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = __shfl_sync(0xffffffffu, v[e], partner);
+    } else {
+      o[0] = v[1]; o[1] = v[0]; o[2] = v[3]; o[3] = v[2];
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int d = d0 + e;
+      if (d < rot) {
+        const bool first = style == 0 ? d < half : (e & 1) == 0;
+        const int i = style == 0 ? (first ? d : d - half) : d >> 1;
+        const float2 c = cs[i];
+        // (u, v) -> (u cos - v sin, v cos + u sin)
+        v[e] = first ? v[e] * c.x - o[e] * c.y : v[e] * c.x + o[e] * c.y;
+      }
+      ss = fmaf(v[e], v[e], ss);
+    }
+    if (unit_norm) {
+#pragma unroll
+      for (int m = LPV / 2; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] *= inv;
+    }
+    if (j < total) {
+      const bool is_q = j < nq;
+      const int jj = is_q ? j : j - nq;
+      const int s = jj % slots;
+      act_t* dst = is_q ? q_out + ((size_t)t * nq + jj) * width
+                        : k_pages + (((size_t)page * nkv + jj / slots) * TL_PAGE + in_page) * width;
+      if (is_q && slots > 1) {
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int other = 0; other < slots; ++other)
+          if (other != s) ra_store4(dst + other * dim + d0, zero);
+      }
+      ra_store4(dst + s * dim + d0, v);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = nx[e];
+  }
+}
+
 extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const float* inv_freq, int rot, int style,
                                               int unit_norm, float eps, void* q_out, void* k_pages, void* v_pages,
                                               const int* token_pos, const int* token_seq, const int* seq_slot,
@@ -281,6 +392,19 @@ extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const flo
   const size_t smem = tile_bytes > token_bytes ? tile_bytes : token_bytes;
   if (T >= 256 && smem <= 48 * 1024) {
     const unsigned blocks = (unsigned)T + (unsigned)((T + 31) / 32) * (unsigned)nv;
+    const bool quads = (dim == 16 || dim == 32 || dim == 64 || dim == 128) && ldz % 4 == 0 && ((uintptr_t)z & 15) == 0 &&
+                       ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && (style != 0 || rot % 8 == 0);
+    if (quads) {
+#define RA_VEC(LPV_)                                                                                                \
+      return tl_launch(rotary_cache_write_vec_kernel<LPV_>, dim3(blocks), dim3(RAM_WARPS * 32), smem, stream, z,   \
+                       ldz, inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, \
+                       token_pos, token_seq, seq_slot, page_table, table_stride, T, nq, nk, nv, vdim, slots)
+      if (dim == 16) RA_VEC(4);
+      if (dim == 32) RA_VEC(8);
+      if (dim == 64) RA_VEC(16);
+      RA_VEC(32);
+#undef RA_VEC
+    }
 #define RA_MANY(R_)                                                                                                  \
     return tl_launch(rotary_cache_write_many_kernel<R_>, dim3(blocks), dim3(RAM_WARPS * 32), smem, stream, z, ldz,  \
                      inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages,         \

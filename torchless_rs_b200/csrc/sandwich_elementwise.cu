@@ -24,13 +24,19 @@ __global__ void norm_add_norm_kernel(const float* __restrict__ y, int ldy, const
   const float* yr = y + (size_t)r * ldy;
   float* xr = x + (size_t)r * H;
   const bool fits = H <= (int)blockDim.x * SW_KEEP;
-  float keep[SW_KEEP];
+  auto weight = [&](const void* w, int i) {
+    return w32 ? ((const float*)w)[i] : __bfloat162float(((const __nv_bfloat16*)w)[i]);
+  };
+  float keep[SW_KEEP], xs[SW_KEEP], wo[SW_KEEP];
   float ss = 0.0f;
   if (fits) {
+    // the stream and the weight are asked for before the first sum, so that they arrive during it
 #pragma unroll
     for (int j = 0; j < SW_KEEP; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       keep[j] = i < H ? yr[i] : 0.0f;
+      xs[j] = i < H ? xr[i] : 0.0f;
+      wo[j] = i < H ? weight(w_out, i) : 0.0f;
       ss = fmaf(keep[j], keep[j], ss);
     }
   } else {
@@ -38,19 +44,23 @@ __global__ void norm_add_norm_kernel(const float* __restrict__ y, int ldy, const
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps_out);
-  auto weight = [&](const void* w, int i) {
-    return w32 ? ((const float*)w)[i] : __bfloat162float(((const __nv_bfloat16*)w)[i]);
-  };
   float s2 = 0.0f;
   if (fits) {
 #pragma unroll
     for (int j = 0; j < SW_KEEP; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       if (i < H) {
-        const float v = xr[i] + keep[j] * inv * weight(w_out, i);
+        const float v = xs[j] + keep[j] * inv * wo[j];
         xr[i] = v;
         keep[j] = v;
         s2 = fmaf(v, v, s2);
+      }
+    }
+    if (w_next != nullptr) {
+#pragma unroll
+      for (int j = 0; j < SW_KEEP; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        wo[j] = i < H ? weight(w_next, i) : 0.0f;
       }
     }
   } else {
@@ -68,7 +78,7 @@ __global__ void norm_add_norm_kernel(const float* __restrict__ y, int ldy, const
 #pragma unroll
     for (int j = 0; j < SW_KEEP; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
-      if (i < H) o[i] = from_f32<act_t>(keep[j] * inv2 * weight(w_next, i));
+      if (i < H) o[i] = from_f32<act_t>(keep[j] * inv2 * wo[j]);
     }
   } else {
     // every thread reads back what it wrote itself
