@@ -99,6 +99,52 @@ CONFIGS = {
 }
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn from `seed`: two to five layers, each with its own mixer (either kind; one to
+    eight heads over any divisor of key/value heads; query sizes 8 to 128 with value sizes that are and are
+    not twice the query's; rotation of all, of a part, of nothing; windows of 1 to 150 and none; caps
+    present and absent) and feed-forward (none, dense, or 4 to 32 experts in 1 to 8 groups with any number
+    kept and chosen, with and without a shared expert).  Scores stay within a few units, as a trained
+    model's do, so that bfloat16 rounding stays within the models' bound."""
+    r = np.random.default_rng(seed)
+
+    def pick(xs):
+        return xs[int(r.integers(0, len(xs)))]
+    width, vocab = pick([64, 128, 192, 320]), pick([97, 300, 1000])
+    layers = []
+    for _ in range(int(r.integers(2, 6))):
+        H = pick([1, 2, 4, 6, 8])
+        G = pick([g for g in (1, 2, 3, 4, 6, 8) if H % g == 0])
+        if r.random() < 0.5:
+            dim = pick([8, 24, 32, 40, 64])
+            vdim = pick([2 * dim, 2 * dim, 24, 40, 64, 128])
+            rot = pick([None, dim, 2 * int(r.integers(1, dim // 2 + 1))])
+            mixer = diff_mixer(H, G, dim, vdim, diff=float(r.uniform(0.1, 0.9)), rot=rot,
+                               base=float(pick([100.0, 10000.0, 5e5])))
+        else:
+            dim = pick([24, 32, 64, 128])
+            vdim = pick([dim, dim, 24, 40, 64])
+            rot = pick([None, dim, 2 * int(r.integers(1, dim // 2 + 1))])
+            mixer = window_mixer(H, G, dim, vdim, window=pick([None, 1, 7, 33, 64, 100, 150]), rot=rot,
+                                 base=float(pick([100.0, 10000.0, 5e5])), scale=float(r.uniform(0.7, 1.5)) * 8.0 / dim,
+                                 softcap=pick([None, 5.0, 20.0, 50.0]))
+        k = r.random()
+        if k < 0.2:
+            mlp = None
+        elif k < 0.55:
+            mlp = dense(pick([64, 200, 384]))
+        else:
+            E = pick([4, 6, 8, 12, 16, 32])
+            count = pick([c for c in (1, 2, 3, 4, 8) if E % c == 0])
+            keep = int(r.integers(1, count + 1))
+            top = int(r.integers(1, min(8, keep * (E // count)) + 1))
+            mlp = moe(pick([16, 32, 64]), E, top, groups=count if r.random() < 0.85 else None, keep=keep,
+                      limit=pick([0.5, 1.0, 7.0]), scale=float(r.uniform(0.5, 3.0)),
+                      shared=(pick([16, 48]), pick([0.7, 3.0])) if r.random() < 0.6 else None)
+        layers.append(layer(mixer, mlp))
+    return config(width, vocab, layers, eps=pick([1e-6, 1e-5]))
+
+
 def tensor_shapes(cfg: dict) -> dict:
     """Tensor names and shapes, as the design lays them out."""
     W, out = cfg["width"], {}

@@ -13,7 +13,7 @@ import torch
 
 from helpers_gpu import assert_close as _assert_close_32
 from plain import rupasun_plain as plain
-from rupasun_tiny import CONFIGS, TModel, make_weights, sure_tokens, tokens_of, write_folder
+from rupasun_tiny import CONFIGS, TModel, make_weights, random_config, sure_tokens, tokens_of, write_folder
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -138,6 +138,38 @@ def test_long_decoding(name):
     assert len(tm.engine._graphs) > 0, "no decode step was replayed from a graph"
     for i in (0, 1):
         assert_close(np.stack(got[i]), tm.reference(reqs[i]), "float32", f"{name} sequence {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [3, 8, 13, 14])
+def test_configurations_drawn_at_random(seed, dtype):
+    """Other sizes, head counts, layer orders, windows and constants than the named configurations have: a whole
+    prompt, a prefix and then token by token, and three unequal requests in one batch that are then decoded
+    together, against the plain implementation."""
+    tm = TModel(random_config(seed), dtype, seed=100 + seed, max_tokens=2048)
+    rng = np.random.default_rng(seed)
+    reqs = [sure_tokens(tm, rng, n) for n in (230, 150, 40)]
+    refs = [tm.reference(q) for q in reqs]
+    s = tm.engine.start_sequences(1)
+    assert_close(tm.step_np(s, [reqs[0]], "all"), refs[0], dtype, f"seed {seed} whole")
+    tm.engine.end_sequences(s)
+    s = tm.engine.start_sequences(1)
+    got = [tm.step_np(s, [reqs[0][:180]], "all")] + [tm.step_np(s, [[t]], "all") for t in reqs[0][180:]]
+    assert_close(np.concatenate(got), refs[0], dtype, f"seed {seed} prefix, then one by one")
+    tm.engine.end_sequences(s)
+    s = tm.engine.start_sequences(3)
+    cut = [len(q) - 20 for q in reqs]
+    first = tm.step_np(s, [q[:c] for q, c in zip(reqs, cut)], "all")
+    rows = [[first[sum(cut[:i]):sum(cut[:i + 1])]] for i in range(3)]
+    for k in range(20):
+        out = tm.step_np(s, [[q[c + k]] for q, c in zip(reqs, cut)], "last")
+        for i in range(3):
+            rows[i].append(out[i:i + 1])
+    tm.engine.end_sequences(s)
+    for i in range(3):
+        assert_close(np.concatenate(rows[i]), refs[i], dtype, f"seed {seed} request {i} of a batch")
+    tm.engine.check_kernels()
+    tm.engine.cache.check()
 
 
 @pytest.mark.parametrize("name", ["P", "R"])
