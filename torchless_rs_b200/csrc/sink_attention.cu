@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 #define SA_THREADS 128
-#define SA_MAX_DIM 256
+#define SA_MAX_DIM 512
 
 // The step's projections (32-bit, one row per token: q heads, k heads, v heads side by side) get
 // their biases; q and k are divided by their root mean square per head and multiplied by a weight
