@@ -189,8 +189,7 @@ __device__ __forceinline__ uint32_t tc_idesc(int n) {   // bf16 x bf16 -> f32, M
 
 // CAP: the scaled scores are capped, s <- cap tanh(s scale / cap), before mask and softmax; `scale_log2` is
 // then log2(e) alone, `cap_c2` = 2 log2(e) scale / cap, and tanh(x) = 1 - 2 / (e^(2x) + 1) by one fast
-// exponential and one fast reciprocal (absolute error about 1e-7; exact at both ends: 2^x overflows to
-// infinity, whose reciprocal is 0, and underflows to 0).
+// exponential and a reciprocal by Newton steps (absolute error about 1e-7; exact at both ends).
 template <bool CAP>
 __global__ void __launch_bounds__(TC_THREADS)
 FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -363,14 +362,28 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
       tc_wait_ld();
       const int key0 = (ps + i) * PAGE;
       if (CAP) {
-        const float m2cap = -2.0f * cap;
+        // cap tanh(x) = cap + 2 cap s with s = -1 / (e^(2x) + 1).  The exponential is the special-function
+        // unit's; the reciprocal is not (that unit is the kernel's bound): s starts from the divisor's bits
+        // (5 % off) and takes three Newton steps, e = 1 + d s, s <- s + s e, two scores per packed
+        // instruction, which leaves 6e-8 of s.  The exponent is held at 60, where tanh is 1 in 32 bits and
+        // the divisor stays finite.
+        const uint64_t c2 = tc_pack2(cap_c2, cap_c2), zero2 = tc_pack2(0.0f, 0.0f), one2 = tc_pack2(1.0f, 1.0f);
+        const uint64_t cap2 = tc_pack2(cap, cap), twocap2 = tc_pack2(2.0f * cap, 2.0f * cap);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          float ra, rb;
-          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(tc_ex2(__uint_as_float(sa[j]) * cap_c2) + 1.0f));
-          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rb) : "f"(tc_ex2(__uint_as_float(sb[j]) * cap_c2) + 1.0f));
-          sa[j] = __float_as_uint(fmaf(m2cap, ra, cap));
-          sb[j] = __float_as_uint(fmaf(m2cap, rb, cap));
+          uint32_t* sc = j < 16 ? sa : sb;
+          const int c = 2 * (j & 15);
+          float x0, x1, d0, d1;
+          tc_unpack2(tc_fma2(tc_pack2(__uint_as_float(sc[c]), __uint_as_float(sc[c + 1])), c2, zero2), x0, x1);
+          const uint64_t d2 = tc_add2(tc_pack2(tc_ex2(fminf(x0, 60.0f)), tc_ex2(fminf(x1, 60.0f))), one2);
+          tc_unpack2(d2, d0, d1);
+          uint64_t s2 = tc_pack2(__uint_as_float(0xFEF311C7u - __float_as_uint(d0)),
+                                 __uint_as_float(0xFEF311C7u - __float_as_uint(d1)));
+#pragma unroll
+          for (int it = 0; it < 3; ++it) s2 = tc_fma2(s2, tc_fma2(d2, s2, one2), s2);
+          tc_unpack2(tc_fma2(twocap2, s2, cap2), x0, x1);
+          sc[c] = __float_as_uint(x0);
+          sc[c + 1] = __float_as_uint(x1);
         }
       }
       // a page that every row of this warp sees whole needs no mask (all but the pages on the
