@@ -230,14 +230,23 @@ class Cache:
         self._of_layer: Dict[int, Union[PagedGroup, StateGroup]] = {}
         # A mixer made of several (branches side by side) asks for several things at once: a tuple
         # of requests, each of which joins the group of its kind under the key (entry, place).
-        self._composite: Dict[int, int] = {}
+        # A branch may itself ask for several things (a tuple inside the tuple): keys grow a place per level,
+        # and `view` hands back tuples of the same shape.
+        self._composite: Dict[int, object] = {}
         by_request: Dict[object, List[object]] = {}
+
+        def walk(req, key):
+            """Files every request of a (nested) tuple under its key; returns the keys in the tuple's shape."""
+            if isinstance(req, (tuple, list)):
+                return tuple(walk(sub, key + (j,)) for j, sub in enumerate(req))
+            if req is None:
+                return None
+            by_request.setdefault(req, []).append(key)
+            return key
+
         for layer, req in enumerate(requests):
             if isinstance(req, (tuple, list)):
-                self._composite[layer] = len(req)
-                for j, sub in enumerate(req):
-                    if sub is not None:
-                        by_request.setdefault(sub, []).append((layer, j))
+                self._composite[layer] = walk(req, (layer,))
             elif req is not None:
                 by_request.setdefault(req, []).append(layer)
         for req, layers in by_request.items():
@@ -352,8 +361,13 @@ class Cache:
     # ---- views ---------------------------------------------------------------------
     def view(self, layer: int):
         if layer in self._composite:
-            keys = [(layer, j) for j in range(self._composite[layer])]
-            return tuple(None if k not in self._of_layer else self._of_layer[k].view(k) for k in keys)
+            def views(keys):
+                if keys is None:
+                    return None
+                if keys and isinstance(keys[0], int):          # a key: (entry, place, ...)
+                    return self._of_layer[keys].view(keys)
+                return tuple(views(k) for k in keys)
+            return views(self._composite[layer])
         g = self._of_layer.get(layer)
         return None if g is None else g.view(layer)
 

@@ -65,6 +65,8 @@ def _register_builtin() -> None:
     register_architecture("Tovapel")(TovapelConfig)
     from .rupasun import RupasunConfig
     register_architecture("Rupasun")(RupasunConfig)
+    from .fezolorn import FezolornConfig
+    register_architecture("Fezolorn")(FezolornConfig)
 
 
 _register_builtin()

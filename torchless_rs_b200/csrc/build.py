@@ -33,7 +33,8 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 
 _CORE_SOURCES = ("elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "branch_elementwise.cu",
                  "latent_attention.cu", "linear_recurrence.cu", "hyper_elementwise.cu", "sink_attention.cu",
-                 "gla_recurrence.cu", "moe.cu", "rotary_attention.cu", "sandwich_elementwise.cu")
+                 "gla_recurrence.cu", "moe.cu", "rotary_attention.cu", "sandwich_elementwise.cu",
+                 "delta_recurrence.cu")
 
 # library name -> (sources, defines)
 LIBRARIES: Dict[str, Tuple[Sequence[str], Sequence[str]]] = {

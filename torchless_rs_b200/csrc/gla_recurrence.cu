@@ -462,23 +462,25 @@ extern "C" long long TL_NAME(tl_gla_scan_scratch)(int T, int B, int heads, int d
 }
 
 // zq, zk, zv: columns of one 32-bit product [T, ld]; za: [T, lda] 32-bit pre-activations of the decay
-// (overwritten with the decays when the step has many tokens per sequence, T > 4 B); bias:
+// (overwritten with the decays when the step has many tokens per sequence, T > 4 B), or, with `given`,
+// the decays themselves, which are only read (lda may then be 0: one row of decays for every token, a
+// recurrence whose decay is a constant of the head); bias:
 // [heads * dim] or null; state: [slots, heads, dim, vdim]; o: [T, ldo]; sequence b owns the tokens
 // seq_start[b] .. seq_start[b + 1] - 1 of the step.
 extern "C" int TL_NAME(tl_gla_scan)(const float* zq, const float* zk, const float* zv, int ld, float* za, int lda,
                                     const float* bias, float tau, float q_scale, float* state, float* o, int ldo,
                                     const int* seq_start, const int* seq_slot, int T, int B, int heads, int dim,
-                                    int vdim, float* scratch, cudaStream_t stream) {
+                                    int vdim, float* scratch, int given, cudaStream_t stream) {
   if (B <= 0 || T <= 0) return 0;
-  if (heads <= 0 || dim <= 0 || vdim <= 0 || !(tau > 0.0f)) return TL_ERR_BAD_ARG;
+  if (heads <= 0 || dim <= 0 || vdim <= 0 || (!given && !(tau > 0.0f))) return TL_ERR_BAD_ARG;
   const int R = (dim + 31) / 32;
   if (heads > 65535 || R > GLA_MAX_R) return TL_ERR_UNSUPPORTED;
   const int per_block = GLA_WARPS * GLA_COLS;
   dim3 grid(B, heads, (vdim + per_block - 1) / per_block);
   if (grid.z > 65535) return TL_ERR_UNSUPPORTED;
-  const float inv_tau = 1.0f / tau;
-  const bool pre = T > 4 * B;
-  if (pre) {
+  const float inv_tau = given ? 1.0f : 1.0f / tau;
+  const bool pre = given || T > 4 * B;
+  if (pre && !given) {
     const size_t total = (size_t)T * heads * dim;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     const int rc = tl_launch(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, za, lda, bias, inv_tau, T,

@@ -327,12 +327,14 @@ extern "C" int TL_NAME(tl_branch_norm_mean)(const float* const* ys, const float*
   return tl_launch(branch_norm_mean_kernel, dim3(T), dim3(row_threads(H)), 0, stream, p, n, H, eps, out, accumulate);
 }
 
-// Per-head output norm with a gate: out[t, h, :] = act( o[t, h, :] / rms * w[:] * silu(g[t, h, :]) ),
-// the norm over the head's `vdim` entries with one weight vector for all heads.  A warp per (t, h).
+// Per-head output norm with a gate: out[t, h, :] = act( o[t, h, :] / rms * w[:] * f(g[t, h, :]) ),
+// the norm over the head's `vdim` entries with one weight vector for all heads; f is silu (gate_act 0)
+// or the sigmoid (1).  A warp per (t, h).  (One "head" of the row's whole width is a norm over the
+// concatenated heads.)
 __global__ void __launch_bounds__(256)
 headnorm_silu_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
                           const float* __restrict__ g, int ldg, act_t* __restrict__ out, int rows, int heads,
-                          int vdim) {
+                          int vdim, int gate_act) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -347,17 +349,19 @@ headnorm_silu_gate_kernel(const float* __restrict__ o, const float* __restrict__
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   for (int i = lane; i < vdim; i += 32) {
     const float z = gate[i];
-    out[(size_t)r * vdim + i] = from_f32<act_t>(src[i] * inv * w[i] * (z / (1.0f + expf(-z))));
+    const float sg = 1.0f / (1.0f + expf(-z));
+    out[(size_t)r * vdim + i] = from_f32<act_t>(src[i] * inv * w[i] * (gate_act == 0 ? z * sg : sg));
   }
 }
 
 extern "C" int TL_NAME(tl_headnorm_silu_gate)(const float* o, const float* w, float eps, const float* g, int ldg,
-                                              void* out, int T, int heads, int vdim, cudaStream_t stream) {
+                                              void* out, int T, int heads, int vdim, int gate_act,
+                                              cudaStream_t stream) {
   if (T <= 0) return 0;
   if (heads < 1 || vdim < 1) return TL_ERR_BAD_ARG;
   const long long rows = (long long)T * heads;
   if (rows > 0x7fffffffLL) return TL_ERR_UNSUPPORTED;
   const unsigned blocks = (unsigned)((rows + 7) / 8);
   return tl_launch(headnorm_silu_gate_kernel, dim3(blocks), dim3(256), 0, stream, o, w, eps, g, ldg, (act_t*)out,
-                   (int)rows, heads, vdim);
+                   (int)rows, heads, vdim, gate_act);
 }

@@ -75,7 +75,7 @@ extern "C" int TL_NAME(tl_latent_prep)(const float* dq, int ld_dq, const float* 
 //   A 32-bit, row stride lda, head h at column h * a_head;  W [heads, N, K] in the activation type;
 //   C row stride ldc, head h at column h * c_head.
 // epilogue 0: C 32-bit = product;  1: C (activation type) = product * sigmoid(G[t, h * N + n]),
-// G 32-bit with row stride ldg (an output gate).
+// G 32-bit with row stride ldg (an output gate), or the product alone where G is null.
 // 64 x 64 tiles, 16 K-elements a step, 256 threads with 4 x 4 outputs each; 32-bit FFMA.
 // ---------------------------------------------------------------------------
 #define HW_BM 64
@@ -133,8 +133,8 @@ headwise_gemm_kernel(const float* __restrict__ A, int lda, int a_head, const act
       if (EPI == 0) {
         ((float*)C)[at] = acc[i][j];
       } else {
-        const float g = G[(size_t)m * ldg + (size_t)h * N + n];
-        ((act_t*)C)[at] = from_f32<act_t>(acc[i][j] * (1.0f / (1.0f + expf(-g))));
+        const float g = G != nullptr ? 1.0f / (1.0f + expf(-G[(size_t)m * ldg + (size_t)h * N + n])) : 1.0f;
+        ((act_t*)C)[at] = from_f32<act_t>(acc[i][j] * g);
       }
     }
   }
@@ -162,8 +162,8 @@ headwise_gemv_kernel(const float* __restrict__ A, int lda, int a_head, const act
     if (EPI == 0) {
       ((float*)C)[at] = acc;
     } else {
-      const float g = G[(size_t)m * ldg + (size_t)h * N + n];
-      ((act_t*)C)[at] = from_f32<act_t>(acc * (1.0f / (1.0f + expf(-g))));
+      const float g = G != nullptr ? 1.0f / (1.0f + expf(-G[(size_t)m * ldg + (size_t)h * N + n])) : 1.0f;
+      ((act_t*)C)[at] = from_f32<act_t>(acc * g);
     }
   }
 }
@@ -172,7 +172,7 @@ extern "C" int TL_NAME(tl_headwise_gemm)(const float* A, int lda, int a_head, co
                                          int c_head, const float* G, int ldg, int M, int N, int K, int heads,
                                          int epilogue, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || heads <= 0) return 0;
-  if (K <= 0 || epilogue < 0 || epilogue > 1 || (epilogue == 1 && G == nullptr)) return TL_ERR_BAD_ARG;
+  if (K <= 0 || epilogue < 0 || epilogue > 1) return TL_ERR_BAD_ARG;
   if (heads > 65535) return TL_ERR_UNSUPPORTED;
   if (M <= 16) {
     dim3 grid((N + 7) / 8, M, heads);
@@ -229,7 +229,7 @@ latent_attn_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, const f
                    const act_t* __restrict__ pages, float* __restrict__ o, const int* __restrict__ token_pos,
                    const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                    const int* __restrict__ page_table, int table_stride, const float* __restrict__ inv_freq,
-                   int heads, int rank, int rot, int dims, int window, float scale) {
+                   const float* __restrict__ sink, int heads, int rank, int rot, int dims, int window, float scale) {
   extern __shared__ float qs[];          // [rank + rot]
   __shared__ float ps[LAT_THREADS];
   __shared__ int pg[LAT_THREADS];
@@ -305,11 +305,13 @@ latent_attn_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, const f
     }
     __syncthreads();   // ps and pg are rewritten by the next chunk
   }
+  // a sink is a key with the score sink[h] (not scaled) and no value: it only enters the denominator
+  const float denom = sink != nullptr ? l_run + expf(sink[h] - m_run) : l_run;
   float* orow = o + ((size_t)t * heads + h) * rank;
 #pragma unroll
   for (int j = 0; j < LAT_MAX_PER_THREAD; ++j) {
     const int d = tid + j * LAT_THREADS;
-    if (d < rank) orow[d] = acc[j] / l_run;
+    if (d < rank) orow[d] = acc[j] / denom;
   }
 }
 
@@ -317,15 +319,15 @@ extern "C" int TL_NAME(tl_latent_attn)(const float* qa, int ld_qa, int qa_head, 
                                        int q_head, int q_off,
                                        const void* pages, float* o, const int* token_pos, const int* token_seq,
                                        const int* seq_slot, const int* page_table, int table_stride,
-                                       const float* inv_freq, int T, int heads, int rank, int rot, int dims,
-                                       int window, float scale, cudaStream_t stream) {
+                                       const float* inv_freq, const float* sink, int T, int heads, int rank,
+                                       int rot, int dims, int window, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (heads <= 0 || rank <= 0 || rot < 0 || dims > rot || (dims & 1)) return TL_ERR_BAD_ARG;
   if (rank > LAT_THREADS * LAT_MAX_PER_THREAD || heads > 65535 || (rank + rot) * sizeof(float) > 40 * 1024)
     return TL_ERR_UNSUPPORTED;
   return tl_launch(latent_attn_kernel, dim3(T, heads), dim3(LAT_THREADS), (size_t)(rank + rot) * sizeof(float),
                    stream, qa, ld_qa, qa_head, q, ldq, q_head, q_off, (const act_t*)pages, o, token_pos, token_seq, seq_slot,
-                   page_table, table_stride, inv_freq, heads, rank, rot, dims, window, scale);
+                   page_table, table_stride, inv_freq, sink, heads, rank, rot, dims, window, scale);
 }
 
 #if TL_DTYPE == 1
@@ -388,7 +390,8 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
                        float* __restrict__ part, const int* __restrict__ token_pos,
                        const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                        const int* __restrict__ page_table, int table_stride, const float* __restrict__ inv_freq,
-                       int T, int heads, int rank, int rot, int dims, int window, float scale, int splits) {
+                       const float* __restrict__ sink, int T, int heads, int rank, int rot, int dims, int window,
+                       float scale, int splits) {
   extern __shared__ __align__(16) unsigned char lm_smem[];
   const int width = rank + rot, pitch = width + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [TB][16][pitch]
@@ -631,7 +634,9 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
     const int row = hg * 16 + g + 8 * r;
     if (splits == 1) {
       if (row >= heads) continue;
-      const float inv = 1.0f / l_run[r];
+      // a sink only enters the denominator (the running maximum is that of the scores times log2(e))
+      const float inv = 1.0f / (sink != nullptr ? l_run[r] + exp2f(sink[row] * 1.4426950408889634f - m_run[r])
+                                                : l_run[r]);
       float* dst = o + ((size_t)t * heads + row) * rank;
 #pragma unroll
       for (int i = 0; i < NTP; ++i) {
@@ -663,8 +668,8 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
 // Merges the parts of a token's keys: out = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
 // (the maxima are those of the scores times log2(e)).
 __global__ void __launch_bounds__(128)
-latent_attn_merge_kernel(const float* __restrict__ part, float* __restrict__ o, int heads, int hpad, int rank,
-                         int splits) {
+latent_attn_merge_kernel(const float* __restrict__ part, float* __restrict__ o, const float* __restrict__ sink,
+                         int heads, int hpad, int rank, int splits) {
   __shared__ float w_s[64];      // the parts' weights (at most 64 parts), then divided by their sum
   __shared__ float scratch[33];
   pdl_wait();
@@ -673,9 +678,11 @@ latent_attn_merge_kernel(const float* __restrict__ part, float* __restrict__ o, 
   const size_t stride = (size_t)(rank + 2);
   const float* src = part + ((size_t)t * hpad + h) * splits * stride;
   const float ms = (int)threadIdx.x < splits ? src[threadIdx.x * stride + rank] : -INFINITY;
-  const float m = block_max(ms, scratch);
+  const float sink2 = sink != nullptr ? sink[h] * 1.4426950408889634f : -INFINITY;
+  const float m = fmaxf(block_max(ms, scratch), sink2);
   const float w = ms != -INFINITY ? exp2f(ms - m) : 0.0f;
-  const float l = block_sum((int)threadIdx.x < splits ? w * src[threadIdx.x * stride + rank + 1] : 0.0f, scratch);
+  float l = block_sum((int)threadIdx.x < splits ? w * src[threadIdx.x * stride + rank + 1] : 0.0f, scratch);
+  if (sink != nullptr) l += exp2f(sink2 - m);        // the sink is counted once, whatever the parts
   if ((int)threadIdx.x < splits) w_s[threadIdx.x] = w / l;
   __syncthreads();
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
@@ -715,8 +722,9 @@ static size_t lm_smem_bytes(int tb, int rank, int rot) {
 extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const float* q, int ldq, int q_head,
                                   int q_off, const void* pages, float* o, float* part, const int* token_pos,
                                   const int* token_seq, const int* seq_slot, const int* page_table,
-                                  int table_stride, const float* inv_freq, int T, int heads, int rank, int rot,
-                                  int dims, int window, float scale, int splits, cudaStream_t stream) {
+                                  int table_stride, const float* inv_freq, const float* sink, int T, int heads,
+                                  int rank, int rot, int dims, int window, float scale, int splits,
+                                  cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rank % 16 || rot % 16 || rank > 512 || rank <= 0 || dims > rot || (dims & 1) || rot > 1024 || splits < 1 ||
       (splits > 1 && part == nullptr))
@@ -740,8 +748,8 @@ extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const
     }                                                                                                        \
     rc = tl_launch(latent_attn_mma_kernel<NTP, TBV>, grid, dim3(LM_THREADS * TBV), smem, stream, qa, ld_qa,  \
                    qa_head, q, ldq, q_head, q_off, (const __nv_bfloat16*)pages, o, part, token_pos, token_seq, \
-                   seq_slot, page_table, table_stride, inv_freq, T, heads, rank, rot, dims, window, scale,   \
-                   splits);                                                                                  \
+                   seq_slot, page_table, table_stride, inv_freq, sink, T, heads, rank, rot, dims, window,    \
+                   scale, splits);                                                                                  \
   }
 #define LM_LAUNCH(NTP) \
   { if (many) LM_LAUNCH_TB(NTP, 4) else LM_LAUNCH_TB(NTP, 1) }
@@ -752,8 +760,8 @@ extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const
 #undef LM_LAUNCH
 #undef LM_LAUNCH_TB
   if (rc != 0 || splits == 1) return rc;
-  return tl_launch(latent_attn_merge_kernel, dim3(T, heads), dim3(128), 0, stream, (const float*)part, o, heads,
-                   groups * 16, rank, splits);
+  return tl_launch(latent_attn_merge_kernel, dim3(T, heads), dim3(128), 0, stream, (const float*)part, o, sink,
+                   heads, groups * 16, rank, splits);
 }
 
 // ---------------------------------------------------------------------------
@@ -830,9 +838,12 @@ headwise_mma_kernel(const float* __restrict__ A, int lda, int a_head, const __nv
     for (int nt = 0; nt < HM_BN / 8; ++nt) {
       const int n = n0 + nt * 8 + qd * 2;
       if (n >= N) continue;          // N is even (checked by the launcher), so n + 1 < N too
-      const float2 gt = *reinterpret_cast<const float2*>(G + (size_t)m * ldg + (size_t)h * N + n);
-      const float v0 = acc[nt][2 * r] * (1.0f / (1.0f + expf(-gt.x)));
-      const float v1 = acc[nt][2 * r + 1] * (1.0f / (1.0f + expf(-gt.y)));
+      float v0 = acc[nt][2 * r], v1 = acc[nt][2 * r + 1];
+      if (G != nullptr) {
+        const float2 gt = *reinterpret_cast<const float2*>(G + (size_t)m * ldg + (size_t)h * N + n);
+        v0 *= 1.0f / (1.0f + expf(-gt.x));
+        v1 *= 1.0f / (1.0f + expf(-gt.y));
+      }
       *reinterpret_cast<uint32_t*>(C + (size_t)m * ldc + (size_t)h * c_head + n) = pack_bf16(v0, v1);
     }
   }
@@ -842,7 +853,7 @@ headwise_mma_kernel(const float* __restrict__ A, int lda, int a_head, const __nv
 extern "C" int tl_headwise_mma(const float* A, int lda, int a_head, const void* W, void* C, int ldc, int c_head,
                                const float* G, int ldg, int M, int N, int K, int heads, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || heads <= 0) return 0;
-  if (K % 8 || N % 2 || lda % 4 || a_head % 4 || ldc % 2 || c_head % 2 || ldg % 2 || G == nullptr ||
+  if (K % 8 || N % 2 || lda % 4 || a_head % 4 || ldc % 2 || c_head % 2 || ldg % 2 ||
       ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)C & 3) || ((uintptr_t)G & 7) || heads > 65535 ||
       (M + HM_BM - 1) / HM_BM > 65535)
     return TL_ERR_UNSUPPORTED;

@@ -140,7 +140,8 @@ class CoreOps:
                      "tl_headnorm_silu_gate", "tl_qk_norm_cache_write", "tl_sink_attn", "tl_gla_scan", "tl_gla_scan_scratch",
                      "tl_moe_route", "tl_moe_plan", "tl_moe_gemm", "tl_moe_combine", "tl_moe_route_grouped",
                      "tl_rotary_cache_write", "tl_diff_heads", "tl_sigmoid_gate", "tl_norm_add_norm", "tl_relu_squared",
-                     "tl_clamped_glu"):
+                     "tl_clamped_glu", "tl_delta_prep", "tl_conv_state_update", "tl_delta_scan", "tl_silu_rows",
+                     "tl_weighted_sum"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
             setattr(self, "_" + base, fn)
@@ -386,13 +387,14 @@ class CoreOps:
             c_int(rot), c_int(dims), _stream()), "latent_prep")
 
     def headwise_gemm(self, a: torch.Tensor, a_head: int, w: torch.Tensor, c: torch.Tensor, c_head: int,
-                      gate: Optional[torch.Tensor] = None) -> None:
+                      gate: Optional[torch.Tensor] = None, act_out: bool = False) -> None:
         """c[t, h * c_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head h; with `gate`
         ([T, heads * N] 32-bit) the result is multiplied by sigmoid(gate) and `c` is of the activation
-        type, else `c` is 32-bit."""
+        type; without a gate `c` is 32-bit, or, with `act_out`, of the activation type."""
+        act_out = act_out or gate is not None
         _need(a, torch.float32, "headwise a", contiguous=False)
         _need(w, self.act_dtype, "headwise w")
-        _need(c, torch.float32 if gate is None else self.act_dtype, "headwise c", contiguous=False)
+        _need(c, self.act_dtype if act_out else torch.float32, "headwise c", contiguous=False)
         heads, N, K = w.shape
         M = a.shape[0]
         if a.stride(1) != 1 or c.stride(1) != 1 or c.shape[0] != M or \
@@ -404,7 +406,7 @@ class CoreOps:
             if gate.shape != (M, heads * N) or gate.stride(1) != 1:
                 raise KernelError("headwise_gemm: the gate must be [rows, heads * outputs]")
             ldg = gate.stride(0)
-        if gate is not None and M > 16 and self.act_dtype == torch.bfloat16:
+        if act_out and M > 16 and self.act_dtype == torch.bfloat16:
             # many rows: the tensor-core kernel, where sizes and alignments allow it
             self.lib.tl_headwise_mma.restype = c_int
             st = self.lib.tl_headwise_mma(_ptr(a), c_int(a.stride(0)), c_int(a_head), _ptr(w), _ptr(c),
@@ -415,21 +417,26 @@ class CoreOps:
                 return
         _check(self._tl_headwise_gemm(_ptr(a), c_int(a.stride(0)), c_int(a_head), _ptr(w), _ptr(c),
                                       c_int(c.stride(0)), c_int(c_head), _ptr(gate), c_int(ldg), c_int(M), c_int(N),
-                                      c_int(K), c_int(heads), c_int(0 if gate is None else 1), _stream()),
+                                      c_int(K), c_int(heads), c_int(1 if act_out else 0), _stream()),
                "headwise_gemm")
 
     def latent_attn(self, qa: torch.Tensor, qa_head: int, q: torch.Tensor, q_head: int, q_off: int,
                     pages: torch.Tensor, out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
                     seq_slot: torch.Tensor, page_table: torch.Tensor, inv_freq: Optional[torch.Tensor], heads: int,
                     rank: int, rot: int, dims: int, window: Optional[int], scale: float,
-                    max_keys: Optional[int] = None, workspace=None) -> None:
+                    max_keys: Optional[int] = None, workspace=None, sink: Optional[torch.Tensor] = None) -> None:
         """out[t, h, :] = softmax over the visible positions of ((qa[t, h] . c + rotate(q_rot[t, h]) . r) *
         scale) times the positions' c; page rows are [c | r].  Head h's latent-space query starts at column
         h * qa_head of `qa`, its part to rotate at column h * q_head + q_off of `q` (one buffer may be both).
 
         In bfloat16 the tensor-core kernel runs where the sizes allow it (rank and rot multiples of 16,
         rank <= 512); `max_keys` (an upper bound of the keys a token of the step sees) lets it cut the keys
-        of a step of few tokens into parts, whose partial sums lie in a buffer of `workspace`."""
+        of a step of few tokens into parts, whose partial sums lie in a buffer of `workspace`.  `sink` (one
+        32-bit number per head) adds exp(sink[h]) to the softmax's denominator, once."""
+        if sink is not None:
+            _need(sink, torch.float32, "sink")
+            if sink.numel() != heads:
+                raise KernelError("latent_attn: one sink per head is needed")
         _need(qa, torch.float32, "latent queries", contiguous=False)
         _need(q, torch.float32, "queries", contiguous=False)
         _need(pages, self.act_dtype, "latent pages")
@@ -456,16 +463,16 @@ class CoreOps:
                     _ptr(qa), c_int(qa.stride(0)), c_int(qa_head), _ptr(q), c_int(q.stride(0)), c_int(q_head),
                     c_int(q_off), _ptr(pages), _ptr(out), _ptr(part), _ptr(token_pos), _ptr(token_seq),
                     _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), _ptr(inv_freq if dims else None),
-                    c_int(T), c_int(heads), c_int(rank), c_int(rot), c_int(dims), c_int(window or 0), c_float(scale),
-                    c_int(splits), _stream()), "latent_attn_mma")
+                    _ptr(sink), c_int(T), c_int(heads), c_int(rank), c_int(rot), c_int(dims), c_int(window or 0),
+                    c_float(scale), c_int(splits), _stream()), "latent_attn_mma")
                 if splits > 1:
                     _check(0, "latent_attn_merge")
                 return
         _check(self._tl_latent_attn(
             _ptr(qa), c_int(qa.stride(0)), c_int(qa_head), _ptr(q), c_int(q.stride(0)), c_int(q_head), c_int(q_off),
             _ptr(pages), _ptr(out), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table),
-            c_int(page_table.stride(0)), _ptr(inv_freq if dims else None), c_int(T), c_int(heads), c_int(rank),
-            c_int(rot), c_int(dims), c_int(window or 0), c_float(scale), _stream()), "latent_attn")
+            c_int(page_table.stride(0)), _ptr(inv_freq if dims else None), _ptr(sink), c_int(T), c_int(heads),
+            c_int(rank), c_int(rot), c_int(dims), c_int(window or 0), c_float(scale), _stream()), "latent_attn")
 
     # ---- gated linear recurrence ------------------------------------------------------------------
     def gated_scan(self, z: torch.Tensor, bias: torch.Tensor, low: torch.Tensor, state: torch.Tensor,
@@ -573,8 +580,10 @@ class CoreOps:
                                          c_int(1 if accumulate else 0), _stream()), "branch_norm_mean")
 
     def headnorm_silu_gate(self, o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor,
-                           out: torch.Tensor, heads: int, vdim: int) -> None:
-        """out[t, h] = act(o[t, h] / rms(o[t, h]) * w * silu(gate[t, h])), the norm over a head's entries."""
+                           out: torch.Tensor, heads: int, vdim: int, sigmoid: bool = False) -> None:
+        """out[t, h] = act(o[t, h] / rms(o[t, h]) * w * silu(gate[t, h])), the norm over a head's entries;
+        with `sigmoid` the gate's function is the sigmoid.  One head of the whole width norms the
+        concatenated heads together."""
         _need(o, torch.float32, "head outputs")
         _need(w, torch.float32, "head norm weight")
         _need(gate, torch.float32, "gate", contiguous=False)
@@ -584,7 +593,8 @@ class CoreOps:
                 w.numel() != vdim:
             raise KernelError("headnorm_silu_gate: sizes do not match")
         _check(self._tl_headnorm_silu_gate(_ptr(o), _ptr(w), c_float(eps), _ptr(gate), c_int(gate.stride(0)),
-                                           _ptr(out), c_int(T), c_int(heads), c_int(vdim), _stream()),
+                                           _ptr(out), c_int(T), c_int(heads), c_int(vdim),
+                                           c_int(1 if sigmoid else 0), _stream()),
                "headnorm_silu_gate")
 
     # ---- attention with a sink, capped scores and a window that keeps the first keys --------------
@@ -649,21 +659,24 @@ class CoreOps:
     def gla_scan(self, zq: torch.Tensor, zk: torch.Tensor, zv: torch.Tensor, za: torch.Tensor,
                  bias: Optional[torch.Tensor], tau: float, q_scale: float, state: torch.Tensor, out: torch.Tensor,
                  seq_start: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int, vdim: int,
-                 workspace=None, chunked: bool = True) -> None:
+                 workspace=None, chunked: bool = True, given: bool = False) -> None:
         """S <- diag(alpha) S + k v^T, o = S^T (q * q_scale) over each sequence's tokens of the step, from and
         into `state` [slots, heads, dim, vdim]; alpha = sigmoid(za + bias)^(1 / tau).  zq, zk, zv are column
         ranges of one 32-bit product (one row stride); `za` may be overwritten with the decays.  Long steps
         run in three passes over chunks of 64 tokens (`chunked`; the same sums in another order), with
-        scratch from `workspace`."""
+        scratch from `workspace`.  With `given`, `za` holds the decays themselves and is only read; it may
+        then be one row [1, heads * dim] that serves every token (a decay that is a constant of the head)."""
         for t, n in ((zq, "q"), (zk, "k"), (zv, "v"), (za, "decay pre-activations")):
             _need(t, torch.float32, "recurrence " + n, contiguous=False)
             if t.stride(1) != 1:
                 raise KernelError("gla_scan: rows must be contiguous")
+        one_row = given and za.shape[0] == 1
         _need(state, torch.float32, "recurrent state")
         _need(out, torch.float32, "recurrence out")
         T = zq.shape[0]
         if not (zq.stride(0) == zk.stride(0) == zv.stride(0)) or zq.shape[1] != heads * dim or \
-                zk.shape[1] != heads * dim or zv.shape[1] != heads * vdim or za.shape != (T, heads * dim) or \
+                zk.shape[1] != heads * dim or zv.shape[1] != heads * vdim or \
+                za.shape != (1 if one_row else T, heads * dim) or \
                 out.shape != (T, heads * vdim) or state.shape[1:] != (heads, dim, vdim):
             raise KernelError("gla_scan: sizes do not match")
         if bias is not None:
@@ -675,16 +688,100 @@ class CoreOps:
         if n:
             scratch = (workspace.get("gla_chunks", (n,), torch.float32) if workspace is not None
                        else torch.empty(n, dtype=torch.float32, device=zq.device))
-        _check(self._tl_gla_scan(_ptr(zq), _ptr(zk), _ptr(zv), c_int(zq.stride(0)), _ptr(za), c_int(za.stride(0)),
+        _check(self._tl_gla_scan(_ptr(zq), _ptr(zk), _ptr(zv), c_int(zq.stride(0)), _ptr(za),
+                                 c_int(0 if one_row else za.stride(0)),
                                  _ptr(bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(out),
                                  c_int(out.stride(0)), _ptr(seq_start), _ptr(seq_slot), c_int(T),
                                  c_int(seq_slot.numel()), c_int(heads), c_int(dim), c_int(vdim), _ptr(scratch),
-                                 _stream()), "gla_scan")
-        if T > 4 * seq_slot.numel():
+                                 c_int(1 if given else 0), _stream()), "gla_scan")
+        if T > 4 * seq_slot.numel() and not given:
             _check(0, "gla_decay")
         if n:
             _check(0, "gla_chunk_carry")
             _check(0, "gla_chunk_apply")
+
+    # ---- the gated delta rule, short convolutions, and mixers side by side with a factor each ----------
+    def delta_prep(self, z: torch.Tensor, taps_w: torch.Tensor, kept: torch.Tensor, y: torch.Tensor,
+                   gates: torch.Tensor, neg_a: torch.Tensor, dt_bias: torch.Tensor, col_b: int, col_a: int,
+                   token_seq: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, kv_heads: int,
+                   heads: int, dim: int, vdim: int, unit_eps: float, q_scale: float) -> None:
+        """From the 32-bit projections `z` (columns q [kv_heads * dim], k [kv_heads * dim], v [heads * vdim],
+        then anything; the pre-activations of beta at `col_b` and of the decay at `col_a`, one per head):
+        y = [q | k | v] after the causal convolution over `taps_w` [channels, taps] (last column the current
+        token's; inputs before the step come from `kept` [slots, taps - 1, channels], oldest first) and silu,
+        q and k divided by sqrt(sum of squares + unit_eps), q times `q_scale`;
+        gates[t] = [beta (heads) | exp(neg_a * softplus(za + dt_bias)) (heads) | k . q (kv_heads)]."""
+        _need(z, torch.float32, "projections", contiguous=False)
+        for t, n in ((taps_w, "convolution taps"), (kept, "kept convolution inputs"), (y, "prepared q, k, v"),
+                     (gates, "gates"), (neg_a, "decay rate"), (dt_bias, "decay bias")):
+            _need(t, torch.float32, n)
+        T = z.shape[0]
+        channels = 2 * kv_heads * dim + heads * vdim
+        taps = taps_w.shape[1]
+        if z.stride(1) != 1 or z.shape[1] < max(channels, col_b + heads, col_a + heads) or \
+                taps_w.shape != (channels, taps) or kept.shape[1:] != (taps - 1, channels) or \
+                y.shape != (T, channels) or gates.shape != (T, 2 * heads + kv_heads) or neg_a.numel() != heads or \
+                dt_bias.numel() != heads:
+            raise KernelError("delta_prep: sizes do not match")
+        _check(self._tl_delta_prep(_ptr(z), c_int(z.stride(0)), _ptr(taps_w), c_int(taps), _ptr(kept), _ptr(y),
+                                   c_int(y.stride(0)), _ptr(gates), _ptr(neg_a), _ptr(dt_bias), c_int(col_b),
+                                   c_int(col_a), _ptr(token_seq), _ptr(seq_start), _ptr(seq_slot), c_int(T),
+                                   c_int(kv_heads), c_int(heads), c_int(dim), c_int(vdim), c_float(unit_eps),
+                                   c_float(q_scale), _stream()), "delta_prep")
+
+    def conv_state_update(self, z: torch.Tensor, kept: torch.Tensor, seq_start: torch.Tensor,
+                          seq_slot: torch.Tensor, channels: int) -> None:
+        """kept[slot] <- the last taps - 1 inputs (the first `channels` columns of `z`) of every sequence of the
+        step, older kept inputs moving up where the step brought fewer tokens."""
+        _need(z, torch.float32, "projections", contiguous=False)
+        _need(kept, torch.float32, "kept convolution inputs")
+        if z.stride(1) != 1 or z.shape[1] < channels or kept.shape[2] != channels:
+            raise KernelError("conv_state_update: sizes do not match")
+        _check(self._tl_conv_state_update(_ptr(z), c_int(z.stride(0)), _ptr(kept), c_int(kept.shape[1] + 1),
+                                          _ptr(seq_start), _ptr(seq_slot), c_int(seq_slot.numel()),
+                                          c_int(channels), _stream()), "conv_state_update")
+
+    def delta_scan(self, y: torch.Tensor, gates: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                   seq_start: torch.Tensor, seq_slot: torch.Tensor, kv_heads: int, heads: int, dim: int,
+                   vdim: int) -> None:
+        """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over each sequence's tokens of the step,
+        from and into `state` [slots, heads, dim, vdim]; `y` and `gates` as `delta_prep` leaves them."""
+        for t, n in ((y, "prepared q, k, v"), (gates, "gates"), (state, "recurrent state"), (out, "recurrence out")):
+            _need(t, torch.float32, n)
+        T = y.shape[0]
+        if y.shape[1] != 2 * kv_heads * dim + heads * vdim or gates.shape != (T, 2 * heads + kv_heads) or \
+                out.shape != (T, heads * vdim) or state.shape[1:] != (heads, dim, vdim):
+            raise KernelError("delta_scan: sizes do not match")
+        _check(self._tl_delta_scan(_ptr(y), c_int(y.stride(0)), _ptr(gates), _ptr(state), _ptr(out),
+                                   c_int(out.stride(0)), _ptr(seq_start), _ptr(seq_slot), c_int(seq_slot.numel()),
+                                   c_int(kv_heads), c_int(heads), c_int(dim), c_int(vdim), _stream()), "delta_scan")
+
+    def silu_rows(self, x: torch.Tensor) -> None:
+        """x <- silu(x) in place; x 32-bit [T, n], rows may be strided."""
+        _need(x, torch.float32, "silu input", contiguous=False)
+        if x.stride(1) != 1:
+            raise KernelError("silu_rows: rows must be contiguous")
+        _check(self._tl_silu_rows(_ptr(x), c_int(x.stride(0)), c_int(x.shape[0]), c_int(x.shape[1]), _stream()),
+               "silu_rows")
+
+    def weighted_sum(self, ys, biases, scales, out: torch.Tensor, accumulate: bool) -> None:
+        """out (+)= sum_b scales[b] * (ys[b] + biases[b]); biases[b] may be None.  Up to four terms, all
+        32-bit [T, n]."""
+        n = len(ys)
+        _need(out, torch.float32, "weighted sum out")
+        for y, b in zip(ys, biases):
+            _need(y, torch.float32, "term")
+            if y.shape != out.shape:
+                raise KernelError("weighted_sum: sizes do not match")
+            if b is not None:
+                _need(b, torch.float32, "term bias")
+                if b.numel() != out.shape[1]:
+                    raise KernelError("weighted_sum: a bias has one entry per column")
+        yp = (c_void_p * n)(*[y.data_ptr() for y in ys])
+        bp = (c_void_p * n)(*[b.data_ptr() if b is not None else None for b in biases])
+        sc = (c_float * n)(*[float(s) for s in scales])
+        _check(self._tl_weighted_sum(yp, bp, sc, c_int(n), _ptr(out), c_int(out.shape[0]), c_int(out.shape[1]),
+                                     c_int(1 if accumulate else 0), _stream()), "weighted_sum")
 
     # ---- mixture of experts ---------------------------------------------------------------------------
     def moe_route(self, z: torch.Tensor, correction: Optional[torch.Tensor], top: int, idx: torch.Tensor,
@@ -707,21 +804,31 @@ class CoreOps:
                            unit_norm: bool, eps: float, q_out: torch.Tensor, k_pages: torch.Tensor,
                            v_pages: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
                            seq_slot: torch.Tensor, page_table: torch.Tensor, nq: int, nk: int, nv: int, dim: int,
-                           vdim: int, slots: int = 1) -> None:
+                           vdim: int, slots: int = 1, bias: Optional[torch.Tensor] = None,
+                           values_are_keys: bool = False) -> None:
         """The projections `z` (32-bit rows: `nq` query vectors and `nk` key vectors of `dim`, then `nv` value
         heads of `vdim`): the first `rot` entries of every query and key vector are rotated by the token's
         position (`style` 0: pairs (i, i + rot/2), 1: pairs (2i, 2i + 1)), then, with `unit_norm`, the vector
         is divided by its root mean square; q goes to `q_out`, k and v into the pages.  With `slots` > 1 a
         key row of the pages holds `slots` key vectors side by side and query vector j becomes a row of that
-        width that is zero outside slot j % slots."""
+        width that is zero outside slot j % slots.  `bias` (32-bit, one number per column of `z`) is added as
+        the columns are read.  With `values_are_keys` `z` holds no value columns: a value head is the key
+        vector of its head as projected (bias included), before rotation and norm."""
         _need(z, torch.float32, "projections", contiguous=False)
         _need(q_out, self.act_dtype, "q out")
         _need(k_pages, self.act_dtype, "k pages")
         _need(v_pages, self.act_dtype, "v pages")
         _need(page_table, torch.int32, "page table")
         T = z.shape[0]
-        cols = (nq + nk) * dim + nv * vdim
+        cols = (nq + nk) * dim + (0 if values_are_keys else nv * vdim)
         width = slots * dim
+        v_col = nq * dim if values_are_keys else (nq + nk) * dim
+        if values_are_keys and (vdim != dim or slots != 1):
+            raise KernelError("rotary_cache_write: values that are the keys have the keys' size")
+        if bias is not None:
+            _need(bias, torch.float32, "projection bias")
+            if bias.numel() != cols:
+                raise KernelError("rotary_cache_write: the bias must have one entry per projected column")
         if z.shape[1] < cols or z.stride(1) != 1 or q_out.shape != (T, nq * width) or nk != nv * slots or \
                 k_pages.shape[1:] != (nv, PAGE, width) or v_pages.shape[1:] != (nv, vdim, PAGE):
             raise KernelError("rotary_cache_write: sizes do not match")
@@ -730,7 +837,8 @@ class CoreOps:
             if inv_freq.numel() != rot // 2:
                 raise KernelError("rotary_cache_write: one inverse frequency per rotated pair is needed")
         _check(self._tl_rotary_cache_write(
-            _ptr(z), c_int(z.stride(0)), _ptr(inv_freq if rot else None), c_int(rot), c_int(style),
+            _ptr(z), c_int(z.stride(0)), _ptr(bias), c_int(v_col), _ptr(inv_freq if rot else None), c_int(rot),
+            c_int(style),
             c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(token_pos),
             _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), c_int(T), c_int(nq),
             c_int(nk), c_int(nv), c_int(dim), c_int(vdim), c_int(slots), _stream()), "rotary_cache_write")

@@ -4,7 +4,10 @@
 //
 //   rotary_cache_write   z (32-bit rows: query vectors, key vectors, value heads side by side)
 //                        -> rotated (and, if asked, unit-normed) q in the activation type, rotated
-//                        k and plain v into the token's place in the pages.
+//                        k and plain v into the token's place in the pages.  `bias` (one number per
+//                        column of z, or null) is added as the columns are read; the value heads
+//                        start at column `v_col`, which may be where the key vectors start (the
+//                        values are then the keys as projected, before rotation and norm).
 //   diff_heads           o = a1 - lambda a2 per head, o / rms(o) * mult.
 //   sigmoid_gate         out *= sigmoid(gate), entry by entry.
 //
@@ -23,7 +26,8 @@
 #define RA_WARPS 4
 
 __global__ void __launch_bounds__(RA_WARPS * 32)
-rotary_cache_write_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ inv_freq, int rot,
+rotary_cache_write_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int v_col,
+                          const float* __restrict__ inv_freq, int rot,
                           int style, int unit_norm, float eps, act_t* __restrict__ q_out,
                           act_t* __restrict__ k_pages, act_t* __restrict__ v_pages,
                           const int* __restrict__ token_pos, const int* __restrict__ token_seq,
@@ -48,7 +52,8 @@ rotary_cache_write_kernel(const float* __restrict__ z, int ldz, const float* __r
   for (int j = blockIdx.y * RA_WARPS + warp; j < nq + nk + nv; j += gridDim.y * RA_WARPS) {
     if (j < nq + nk) {
       const float* src = row + (size_t)j * dim;
-      for (int d = lane; d < dim; d += 32) mine[d] = src[d];
+      const float* bj = bias != nullptr ? bias + (size_t)j * dim : nullptr;
+      for (int d = lane; d < dim; d += 32) mine[d] = src[d] + (bj != nullptr ? bj[d] : 0.0f);
       __syncwarp();
       float ss = 0.0f;
       float keep[RA_MAX_DIM / 32];
@@ -103,9 +108,11 @@ rotary_cache_write_kernel(const float* __restrict__ z, int ldz, const float* __r
       __syncwarp();     // `mine` is rewritten by the warp's next vector
     } else {
       const int g = j - nq - nk;
-      const float* src = row + (size_t)(nq + nk) * dim + (size_t)g * vdim;
+      const size_t col = (size_t)v_col + (size_t)g * vdim;
+      const float* src = row + col;
       act_t* dst = v_pages + ((size_t)page * nv + g) * vdim * TL_PAGE + in_page;
-      for (int d = lane; d < vdim; d += 32) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(src[d]);
+      for (int d = lane; d < vdim; d += 32)
+        dst[(size_t)d * TL_PAGE] = from_f32<act_t>(src[d] + (bias != nullptr ? bias[col + d] : 0.0f));
     }
   }
 }
@@ -132,6 +139,17 @@ __device__ __forceinline__ void ra_store4(__nv_bfloat16* p, const float (&v)[4])
   *reinterpret_cast<uint2*>(p) = u;
 }
 
+// Four columns of a row of projections from column `at` on, with the columns' bias if there is one.
+__device__ __forceinline__ void ra_load4_biased(const float* row, const float* bias, size_t at, float (&v)[4]) {
+  ra_load4(row + at, v);
+  if (bias != nullptr) {
+    float b[4];
+    ra_load4(bias + at, b);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] += b[e];
+  }
+}
+
 // The same for steps of many tokens.  Two kinds of block in one launch:
 //  - blockIdx.x < T: one token.  The cosines and sines of its position are computed once (one per
 //    rotated pair) into shared memory; then a warp per query or key vector, the warp's next vector
@@ -142,7 +160,8 @@ __device__ __forceinline__ void ra_store4(__nv_bfloat16* p, const float (&v)[4])
 #define RAM_WARPS 8
 template <int R>
 __global__ void __launch_bounds__(RAM_WARPS * 32)
-rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ inv_freq, int rot,
+rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int v_col,
+                               const float* __restrict__ inv_freq, int rot,
                                int style, int unit_norm, float eps, act_t* __restrict__ q_out,
                                act_t* __restrict__ k_pages, act_t* __restrict__ v_pages,
                                const int* __restrict__ token_pos, const int* __restrict__ token_seq,
@@ -157,10 +176,11 @@ rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float
     const int tile = blockIdx.x - T;
     const int t0 = (tile / nv) * 32, g = tile % nv;
     const int nt = min(32, T - t0);
-    const float* src = z + (size_t)(nq + nk) * dim + (size_t)g * vdim;
+    const size_t col = (size_t)v_col + (size_t)g * vdim;
+    const float* src = z + col;
     for (int idx = threadIdx.x; idx < nt * vdim; idx += blockDim.x) {
       const int tt = idx / vdim, d = idx - tt * vdim;
-      ra_sm[tt * (vdim + 1) + d] = src[(size_t)(t0 + tt) * ldz + d];
+      ra_sm[tt * (vdim + 1) + d] = src[(size_t)(t0 + tt) * ldz + d] + (bias != nullptr ? bias[col + d] : 0.0f);
     }
     __syncthreads();
     if (lane < nt) {
@@ -197,7 +217,7 @@ rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int d = lane + 32 * r;
-      cur[r] = d < dim ? row[(size_t)j * dim + d] : 0.0f;
+      cur[r] = d < dim ? row[(size_t)j * dim + d] + (bias != nullptr ? bias[(size_t)j * dim + d] : 0.0f) : 0.0f;
     }
   }
   for (; j < nq + nk; j += RAM_WARPS) {
@@ -206,7 +226,7 @@ rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const int d = lane + 32 * r;
-        nxt[r] = d < dim ? row[(size_t)jn * dim + d] : 0.0f;
+        nxt[r] = d < dim ? row[(size_t)jn * dim + d] + (bias != nullptr ? bias[(size_t)jn * dim + d] : 0.0f) : 0.0f;
       }
     }
 #pragma unroll
@@ -271,7 +291,8 @@ rotary_cache_write_many_kernel(const float* __restrict__ z, int ldz, const float
 // (pairs (i, i + rot/2); rot a multiple of 8), so nothing is staged in shared memory but the sines.
 template <int LPV>
 __global__ void __launch_bounds__(RAM_WARPS * 32)
-rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ inv_freq, int rot,
+rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int v_col,
+                              const float* __restrict__ inv_freq, int rot,
                               int style, int unit_norm, float eps, act_t* __restrict__ q_out,
                               act_t* __restrict__ k_pages, act_t* __restrict__ v_pages,
                               const int* __restrict__ token_pos, const int* __restrict__ token_seq,
@@ -287,10 +308,11 @@ rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float*
     const int tile = blockIdx.x - T;
     const int t0 = (tile / nv) * 32, g = tile % nv;
     const int nt = min(32, T - t0);
-    const float* src = z + (size_t)(nq + nk) * dim + (size_t)g * vdim;
+    const size_t col = (size_t)v_col + (size_t)g * vdim;
+    const float* src = z + col;
     for (int idx = threadIdx.x; idx < nt * vdim; idx += blockDim.x) {
       const int tt = idx / vdim, d = idx - tt * vdim;
-      ra_sm[tt * (vdim + 1) + d] = src[(size_t)(t0 + tt) * ldz + d];
+      ra_sm[tt * (vdim + 1) + d] = src[(size_t)(t0 + tt) * ldz + d] + (bias != nullptr ? bias[col + d] : 0.0f);
     }
     __syncthreads();
     if (lane < nt) {
@@ -311,7 +333,7 @@ rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float*
   // the first vectors are on their way while the sines are computed
   int j = warp * VPW + sub;
   float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  if (j < total) ra_load4(row + (size_t)j * dim + d0, v);
+  if (j < total) ra_load4_biased(row, bias, (size_t)j * dim + d0, v);
   float2* cs = reinterpret_cast<float2*>(ra_sm);            // [half] (cosine, sine)
   const float fpos = (float)pos;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -330,7 +352,7 @@ rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float*
   for (int j0 = warp * VPW; j0 < total; j0 += RAM_WARPS * VPW) {
     j = j0 + sub;
     const int jn = j + RAM_WARPS * VPW;
-    if (jn < total) ra_load4(row + (size_t)jn * dim + d0, nx);
+    if (jn < total) ra_load4_biased(row, bias, (size_t)jn * dim + d0, nx);
     float o[4];
     if (style == 0) {
 #pragma unroll
@@ -376,14 +398,15 @@ rotary_cache_write_vec_kernel(const float* __restrict__ z, int ldz, const float*
   }
 }
 
-extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const float* inv_freq, int rot, int style,
+extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const float* bias, int v_col,
+                                              const float* inv_freq, int rot, int style,
                                               int unit_norm, float eps, void* q_out, void* k_pages, void* v_pages,
                                               const int* token_pos, const int* token_seq, const int* seq_slot,
                                               const int* page_table, int table_stride, int T, int nq, int nk,
                                               int nv, int dim, int vdim, int slots, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nq < 1 || nk < 1 || nv < 1 || dim < 1 || vdim < 1 || slots < 1 || nq % slots || nk % slots ||
-      nk / slots != nv || rot < 0 || rot > dim || (rot & 1) || (rot > 0 && inv_freq == nullptr))
+      nk / slots != nv || rot < 0 || rot > dim || (rot & 1) || (rot > 0 && inv_freq == nullptr) || v_col < 0)
     return TL_ERR_BAD_ARG;
   if (dim > RA_MAX_DIM) return TL_ERR_UNSUPPORTED;
   const int vectors = nq + nk + nv;
@@ -393,11 +416,12 @@ extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const flo
   if (T >= 256 && smem <= 48 * 1024) {
     const unsigned blocks = (unsigned)T + (unsigned)((T + 31) / 32) * (unsigned)nv;
     const bool quads = (dim == 16 || dim == 32 || dim == 64 || dim == 128) && ldz % 4 == 0 && ((uintptr_t)z & 15) == 0 &&
-                       ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && (style != 0 || rot % 8 == 0);
+                       ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && (style != 0 || rot % 8 == 0) &&
+                       ((uintptr_t)bias & 15) == 0;
     if (quads) {
 #define RA_VEC(LPV_)                                                                                                \
       return tl_launch(rotary_cache_write_vec_kernel<LPV_>, dim3(blocks), dim3(RAM_WARPS * 32), smem, stream, z,   \
-                       ldz, inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, \
+                       ldz, bias, v_col, inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, \
                        token_pos, token_seq, seq_slot, page_table, table_stride, T, nq, nk, nv, vdim, slots)
       if (dim == 16) RA_VEC(4);
       if (dim == 32) RA_VEC(8);
@@ -407,7 +431,7 @@ extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const flo
     }
 #define RA_MANY(R_)                                                                                                  \
     return tl_launch(rotary_cache_write_many_kernel<R_>, dim3(blocks), dim3(RAM_WARPS * 32), smem, stream, z, ldz,  \
-                     inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages,         \
+                     bias, v_col, inv_freq, rot, style, unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages,         \
                      token_pos, token_seq, seq_slot, page_table, table_stride, T, nq, nk, nv, dim, vdim, slots)
     if (dim <= 32) RA_MANY(1);
     if (dim <= 64) RA_MANY(2);
@@ -416,7 +440,7 @@ extern "C" int TL_NAME(tl_rotary_cache_write)(const float* z, int ldz, const flo
 #undef RA_MANY
   }
   const dim3 grid(T, (vectors + RA_WARPS - 1) / RA_WARPS);
-  return tl_launch(rotary_cache_write_kernel, grid, dim3(RA_WARPS * 32), 0, stream, z, ldz, inv_freq, rot, style,
+  return tl_launch(rotary_cache_write_kernel, grid, dim3(RA_WARPS * 32), 0, stream, z, ldz, bias, v_col, inv_freq, rot, style,
                    unit_norm, eps, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, token_pos, token_seq, seq_slot,
                    page_table, table_stride, nq, nk, nv, dim, vdim, slots);
 }

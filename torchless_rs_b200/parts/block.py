@@ -72,6 +72,24 @@ class PreNormBlock:
         return c3 if (c3 is not None and c3.valid) else None
 
 
+@register_block("prenorm_mixer_only")
+class PreNormMixerBlock:
+    """The pre-norm block of a layer without a feed-forward: x += mixer(norm1(x))."""
+    norm_roles = ("mixer_norm",)
+
+    def __init__(self, spec, rt: Runtime, mixer, feed_forward, norms):
+        self.rt = rt
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = dict(norms)
+        self.mixer_norm = norms["mixer_norm"]
+
+    def forward(self, x: torch.Tensor, batch) -> None:
+        rt = self.rt
+        xn = rt.workspace.get("block_normed", x.shape, rt.act_dtype)
+        self.mixer.forward(self.mixer_norm(x, xn), x, batch)
+
+
 class StreamCopy:
     """What a branch-norm block hands to the next one: the stream in the activation type, as the
     kernel that last changed the stream wrote it.  (`valid` is False so that a block that expects the

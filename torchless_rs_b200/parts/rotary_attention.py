@@ -1,4 +1,4 @@
-"""Two softmax attentions with grouped key/value heads whose queries and keys are rotated by position
+"""Softmax attentions with grouped key/value heads whose queries and keys are rotated by position
 on their first `rot_dims` entries (the pairing and the frequencies come from the layer's position
 part), over the paged cache.
 
@@ -15,7 +15,14 @@ twice the size and read every key and every value once per group.
     score = cap tanh(scale (q_i . k_j) / cap),   j visible iff 0 <= i - j < window
     out = sigmoid(W_g h) * concatenated heads     (entry by entry, h the mixer's input)
 
-Both: one stacked product for the projections of the input (32-bit), one kernel that rotates, norms
+`sink_rotary_attention`: optionally biased projections, optionally no value projection at all (a
+head's values are its keys as projected, bias included, before rotation and norm), queries and keys
+divided by their root mean square after the rotation if asked,
+    score = scale (q_i . k_j),   j visible iff 0 <= i - j < window,
+    p(i, j) = exp(score(i, j)) / (sum over visible j' of exp(score(i, j')) + exp(sink_head))
+    out = W_o (concatenated heads) + b_o
+
+All: one stacked product for the projections of the input (32-bit), one kernel that rotates, norms
 and writes q and the token's k and v into the pages, attention from pages only (so a position's
 result does not depend on the step that computes it), a closing kernel, W_o.  Attention runs on the
 kernels of the plain rotary attention where these take it (bfloat16, a key row as wide as a value row,
@@ -42,6 +49,8 @@ class _RotaryAttention:
     can_overwrite = True
     slots = 1            # query/key maps per head
     unit_norm = False    # q and k divided by their root mean square after the rotation
+    proj_bias = None     # 32-bit, one number per column of the stacked projections (None: no bias)
+    values_are_keys = False   # no value projection: a head's values are its keys as projected
 
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime, position=None):
         p = spec.params
@@ -96,19 +105,19 @@ class _RotaryAttention:
         rt.ops.rotary_cache_write(z, pos.inv_freq if self.rot else None, self.rot, pos.style if self.rot else 0,
                                   self.unit_norm, self.eps, q, c.k_pages, c.v_pages, batch.token_pos,
                                   batch.token_seq, batch.seq_slot, c.page_table, H * S, G * S, G, self.dim,
-                                  self.vdim, S)
+                                  self.vdim, S, bias=self.proj_bias, values_are_keys=self.values_are_keys)
         return z, q
 
-    def _attend(self, q, out, batch, softcap):
+    def _attend(self, q, out, batch, softcap, sink=None):
         c = self.cache
-        if self.fast is not None:
+        if self.fast is not None and sink is None:
             H = self.nh * self.slots
             if softcap is None:
                 if self.fast.run(q, c, out, batch, H, self.nkv, self.window, self.scale, self.rt.workspace):
                     return
             elif self.fast.run_capped(q, c, out, batch, H, self.nkv, self.window, self.scale, softcap):
                 return
-        run_attention(self.rt.ops, q, c.k_pages, c.v_pages, None, None, out, batch.token_pos, batch.token_seq,
+        run_attention(self.rt.ops, q, c.k_pages, c.v_pages, None, sink, out, batch.token_pos, batch.token_seq,
                       batch.seq_slot, c.page_table, self.nh * self.slots, self.nkv, self.width, self.vdim,
                       self.window, 0, self.scale, softcap, batch, self.rt.workspace)
 
@@ -199,3 +208,76 @@ class GatedWindowAttention(_RotaryAttention):
         self._attend(q, out, batch, self.softcap)
         rt.ops.sigmoid_gate(out, z[:, g_off:])
         self.matmul(out, self.w_o, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
+
+
+@register_mixer("sink_rotary_attention")
+class SinkRotaryAttention(_RotaryAttention):
+    """Parameters: `hidden_size`, `heads`, `kv_heads`, `dim`, `vdim`, `rot_dims`, `scale`, `window` (None: all
+    keys), `eps` (of the query and key norms), `unit_norm` (queries and keys divided by their root mean square
+    after the rotation), `sink` (a learned logit per head in the denominator), `bias` (q, k, v and o have
+    biases, stored under the tensor's name with `.b`), `values_are_keys` (no v: `vdim` must equal `dim`).
+    Tensors under the prefix: q, k, [v], o, [q.b, k.b, v.b, o.b], [sink].
+
+    `output_bias` is the output projection's bias (or None); `forward(..., defer_bias=True)` leaves it out, for
+    a caller that adds it where it sums this mixer's output with others'."""
+
+    def __init__(self, spec: PartSpec, prefix: str, rt: Runtime, position=None):
+        p = spec.params
+        self.unit_norm = bool(p.get("unit_norm", False))
+        self.values_are_keys = bool(p.get("values_are_keys", False))
+        super().__init__(spec, prefix, rt, position)
+        self.window = int(p["window"]) if p.get("window") else None
+        self.has_sink = bool(p.get("sink", False))
+        self.has_bias = bool(p.get("bias", False))
+        if self.values_are_keys and self.vdim != self.dim:
+            raise ValueError(f"values that are the keys have the keys' size {self.dim}, not {self.vdim}")
+        self.sink = None
+        self.output_bias = None
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
+        p = spec.params
+        hidden, H, G, dim, vdim = (int(p[k]) for k in ("hidden_size", "heads", "kv_heads", "dim", "vdim"))
+        std = hidden ** -0.5
+        out = {f"{prefix}.q": TensorSpec((H * dim, hidden), init=(std, 0.0)),
+               f"{prefix}.k": TensorSpec((G * dim, hidden), init=(std, 0.0)),
+               f"{prefix}.o": TensorSpec((hidden, H * vdim), init=((H * vdim) ** -0.5, 0.0))}
+        if not p.get("values_are_keys"):
+            out[f"{prefix}.v"] = TensorSpec((G * vdim, hidden), init=(std, 0.0))
+        if p.get("bias"):
+            out[f"{prefix}.q.b"] = TensorSpec((H * dim,), init=(0.1, 0.0))
+            out[f"{prefix}.k.b"] = TensorSpec((G * dim,), init=(0.1, 0.0))
+            out[f"{prefix}.o.b"] = TensorSpec((hidden,), init=(0.1, 0.0))
+            if not p.get("values_are_keys"):
+                out[f"{prefix}.v.b"] = TensorSpec((G * vdim,), init=(0.1, 0.0))
+        if p.get("sink"):
+            out[f"{prefix}.sink"] = TensorSpec((H,), init=(1.0, 0.0))
+        return out
+
+    def load(self, weights: Dict[str, torch.Tensor]) -> None:
+        p, rt = self.prefix, self.rt
+        names = ["q", "k"] + ([] if self.values_are_keys else ["v"])
+        self.w_in = rt.stack([weights[f"{p}.{n}"] for n in names])
+        self.w_o = rt.matrix(weights[f"{p}.o"])
+        f32 = lambda t: t.to(device=rt.device, dtype=torch.float32).contiguous()
+        if self.has_bias:
+            self.proj_bias = torch.cat([f32(weights[f"{p}.{n}.b"]) for n in names])
+            self.output_bias = f32(weights[f"{p}.o.b"])
+        if self.has_sink:
+            self.sink = f32(weights[f"{p}.sink"])
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, batch, emit=None, overwrite: bool = False,
+                defer_bias: bool = False) -> None:
+        rt, ws = self.rt, self.rt.workspace
+        T = residual.shape[0]
+        H, G, dim, vdim = self.nh, self.nkv, self.dim, self.vdim
+        cols = (H + G) * dim + (0 if self.values_are_keys else G * vdim)
+        _, q = self._project_and_write(xn, batch, cols)
+        out = ws.get("rot_attn_out", (T, H * vdim), rt.act_dtype)
+        self._attend(q, out, batch, None, sink=self.sink)
+        if self.output_bias is None or defer_bias:
+            self.matmul(out, self.w_o, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
+            return
+        y = residual if overwrite else ws.get("rot_attn_proj", (T, self.hidden), torch.float32)
+        self.matmul(out, self.w_o, y, ops.MODE_STORE_F32)
+        rt.ops.weighted_sum([y], [self.output_bias], [1.0], residual, accumulate=not overwrite)
