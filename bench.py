@@ -280,9 +280,9 @@ def reference_arm(args) -> int:
 
 
 def design_arm(args) -> int:
-    """`--design kikopel|tovapel|rupasun`: prefill and decode throughput of that design at layer sizes of a real
-    model (random weights), beside Mistral (the closest existing model) at equal width, heads, layers,
-    feed-forward and window, and every kernel of the design alone against its roofline beside the like
+    """`--design kikopel|tovapel|rupasun|fezolorn`: prefill and decode throughput of that design at layer sizes of a real
+    model (random weights), beside the closest existing model (Mistral; for fezolorn the third design, whose layers
+    also run attention with a sink beside a linear recurrence) at equal width, heads, layers, feed-forward and window, and every kernel of the design alone against its roofline beside the like
     kernel of the Mistral path.  One JSON line; the default workload is not touched."""
     import torch
     import torchless_rs_b200 as tl
@@ -293,10 +293,11 @@ def design_arm(args) -> int:
     T, B, ctx = PREFILL_TOKENS, args.batch or 8, 2048
     design = args.design
     sizes = {"kikopel": measure.KIKOPEL_SIZES, "tovapel": measure.TOVAPEL_SIZES,
-             "rupasun": measure.RUPASUN_SIZES}[design]
+             "rupasun": measure.RUPASUN_SIZES, "fezolorn": measure.FEZOLORN_SIZES}[design]
     configs = {"kikopel": (measure.kikopel_config, measure.mistral_like, measure.kikopel_kernels),
                "tovapel": (measure.tovapel_config, measure.tovapel_like, measure.tovapel_kernels),
-               "rupasun": (measure.rupasun_config, measure.rupasun_like, measure.rupasun_kernels)}[design]
+               "rupasun": (measure.rupasun_config, measure.rupasun_like, measure.rupasun_kernels),
+               "fezolorn": (measure.fezolorn_config, measure.fezolorn_like, measure.fezolorn_kernels)}[design]
     out = {"design": design, "sizes": dict(sizes[size]), "layers": L, "dtype": "bf16",
            "data": "synthetic: random weights, fixed token ids", "prefill_tokens": T, "decode_batch": B,
            "decode_context": ctx, "steps": args.steps, "warmup": args.warmup}
@@ -304,7 +305,9 @@ def design_arm(args) -> int:
     clocks.start()
     t0 = None
     greedy = SamplingParams.greedy()
-    for name, cfg in ((design, configs[0](size, L)), ("mistral", configs[1](size, L))):
+    like = configs[1](size, L)
+    like_name = "mistral" if "architectures" in like else str(like.get("architecture", "like")).lower()
+    for name, cfg in ((design, configs[0](size, L)), (like_name, like)):
         model = tl.from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=B * (ctx + 64),
                                max_batch=B, max_seq_len=ctx + 64)
         eng = model.engine
@@ -342,7 +345,7 @@ def design_arm(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["kikopel", "tovapel", "rupasun"],
+    ap.add_argument("--design", default=None, choices=["kikopel", "tovapel", "rupasun", "fezolorn"],
                     help="measure another design beside Mistral at equal sizes instead of the default workload")
     ap.add_argument("--design-size", default="1b", choices=["1b", "7b"])
     ap.add_argument("--gpus", type=int, default=1)

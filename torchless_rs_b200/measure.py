@@ -713,6 +713,209 @@ def rupasun_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
         report("  like: moe_route (Tovapel)", case, us, n_tok * (E * 4.0 + top * 8.0), 0.0)
     return rows
 
+# Layer sizes at which the Fezolorn kernels are measured: the width, heads and feed-forward of a 1B- and a
+# 7B-class decoder; the three mixers in turn.  Attention whose values are its keys with a quarter as many
+# key/value heads, half of each head rotated, a window of 4096; the delta rule with half as many query/key
+# heads as value heads and a state of 64 x 128 per head (the state of the closest model's gated linear
+# attention); lightning attention with the same state; latents of the sizes of the second design.
+FEZOLORN_SIZES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, window=4096, ff=5632, r_heads=16, r_kv_heads=8, r_dim=64,
+               r_vdim=128, conv=4, l_heads=16, l_dim=64, l_vdim=128, m_heads=16, m_dim=128, m_rot=64, m_vdim=128,
+               q_rank=768, kv_rank=512, vocab=32000),
+    "7b": dict(width=4096, heads=32, kv_heads=8, dim=128, window=4096, ff=14336, r_heads=32, r_kv_heads=16, r_dim=64,
+               r_vdim=128, conv=4, l_heads=32, l_dim=64, l_vdim=128, m_heads=32, m_dim=128, m_rot=64, m_vdim=128,
+               q_rank=1536, kv_rank=512, vocab=32000),
+}
+
+
+def fezolorn_config(size: str, layers: int) -> dict:
+    """config.json of a Fezolorn model of `layers` layers at these sizes: parallel, lightning, latent in turn."""
+    z = FEZOLORN_SIZES[size]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "scale": 1.0 / math.sqrt(z["dim"]) * 8.0, "mask": {"size": z["window"]},
+                 "rot": {"base": 500000.0, "dims": z["dim"] // 2,
+                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+        "right": {"heads": z["r_heads"], "kv_heads": z["r_kv_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"],
+                  "conv": z["conv"]},
+        "left_scale": 1.0, "right_scale": 1.0}}
+    n = z["l_heads"]
+    lig = {"type": "lightning", "mlp": mlp, "mixer": {
+        "heads": n, "dim": z["l_dim"], "vdim": z["l_vdim"], "decay": [math.exp(-2.0 ** (-8.0 * (i + 1) / n)) for i in range(n)]}}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": z["m_heads"], "dim": z["m_dim"], "rot_dim": z["m_rot"], "vdim": z["m_vdim"], "q_rank": z["q_rank"],
+        "kv_rank": z["kv_rank"], "rot": {"base": 500000.0, "dims": z["m_rot"]},
+        "scale": 1.0 / math.sqrt(z["m_dim"] + z["m_rot"])}}
+    return {"architecture": "Fezolorn", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-6},
+            "max_position_embeddings": 32768, "layers": [(par, lig, lat)[i % 3] for i in range(layers)]}
+
+
+def fezolorn_like(size: str, layers: int) -> dict:
+    """The closest existing model at equal size: the third design (attention with a sink beside gated linear
+    attention in every layer) with one stream, dense feed-forwards, and the same width, heads, key/value heads,
+    recurrent state, feed-forward and window."""
+    z = FEZOLORN_SIZES[size]
+    mixer = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                      "scale": 1.0 / math.sqrt(z["dim"]), "mask": {"size": z["window"], "keep_first": 0}},
+             "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "tau": 16.0, "rank": 16}}
+    return {"architecture": "Tovapel", "width": z["width"], "vocab": z["vocab"], "streams": 1,
+            "norm": {"eps": 1e-5}, "max_position_embeddings": 32768,
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["ff"]}} for _ in range(layers)]}
+
+
+def fezolorn_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) -> list:
+    """Every kernel that the Fezolorn design added or changed, alone at the sizes `size`, for a prompt of T tokens
+    and for a decode step of B sequences at a context of `ctx`, beside the like kernel of the closest model at
+    equal sizes.  Rows and roofline as `kikopel_kernels` defines them."""
+    import json
+    import os
+    from .csrc import ops
+    from .parts.runtime import Workspace
+    from .parts.sink_attention import run_attention
+    z = FEZOLORN_SIZES[size]
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.isfile(pk):
+        peaks.update(json.load(open(pk)))
+    o = ops.core_ops(torch.bfloat16)
+    dev, bf = "cuda", torch.bfloat16
+    H, G, dim, W = z["heads"], z["kv_heads"], z["dim"], z["width"]
+    rows = []
+
+    def report(name, case, us, byts, flops):
+        t_mem, t_fl = byts / (peaks["hbm_gbs"] * 1e3), flops / (peaks["bf16_tflops"] * 1e6)     # microseconds
+        frac = max(t_mem, t_fl) / us
+        rows.append({"kernel": name, "case": case, "us": round(us, 2), "roofline_frac": round(frac, 4),
+                     "bound": "memory" if t_mem >= t_fl else "tensor"})
+        print(f"{name:34s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})", file=file)
+
+    ws = Workspace(torch.device("cuda"))
+    for case, n_tok, seqs, past in ((f"prompt {T}", T, 1, 0), (f"decode {B} x {ctx}", B, B, ctx - 1)):
+        per = n_tok // seqs
+        few = max(2, iters // 8) if n_tok > 64 else iters
+        pos = torch.cat([torch.arange(past, past + per, dtype=torch.int32) for _ in range(seqs)]).to(dev)
+        seq = torch.arange(seqs, dtype=torch.int32).repeat_interleave(per).to(dev)
+        start = (torch.arange(seqs + 1, dtype=torch.int32) * per).to(dev)
+        seen = sum(min(p + 1, z["window"]) for p in range(past, past + per)) * seqs
+        kp, vp, table, slot = _paged(seqs, past + per, G, dim)
+        lens = torch.full((seqs,), past + per, dtype=torch.int32, device=dev)
+        # --- attention with a sink (no gate, no cap), beside the closest model's call of the same kernels
+        q = torch.randn((n_tok, H * dim), device=dev, dtype=bf)
+        out = torch.empty((n_tok, H * dim), device=dev, dtype=bf)
+        gate, sink = torch.randn((n_tok, H), device=dev), torch.zeros(H, device=dev)
+
+        class _B:      # what the kernel choice reads of a step
+            n_tokens, n_seqs, is_decode, max_len, seq_start, seq_len, seq_slot = n_tok, seqs, per == 1, past + per, start, lens, slot
+        cache_b = 2.0 * seqs * min(past + per, z["window"]) * G * 2 * dim
+        us = _time(lambda: run_attention(o, q, kp, vp, None, sink, out, pos, seq, slot, table, H, G, dim, dim,
+                                         z["window"], 0, 0.7, None, _B, ws), few)
+        report("sink_attn (sink only)", case, us, cache_b + n_tok * H * dim * 4.0, 4.0 * H * dim * seen)
+        us = _time(lambda: run_attention(o, q, kp, vp, gate, sink, out, pos, seq, slot, table, H, G, dim, dim,
+                                         z["window"], 4, 0.088, 50.0, _B, ws), few)
+        report("  like: sink_attn (third design)", case, us, cache_b + n_tok * H * dim * 4.0, 4.0 * H * dim * seen)
+        # --- bias, rotation, unit norm and cache write with the keys as values, beside the closest model's
+        # bias, norm and cache write
+        cols = (H + G) * dim
+        zq = torch.randn((n_tok, cols + G * dim + H), device=dev)
+        bias = torch.zeros(cols, device=dev)
+        inv = torch.tensor([5e5 ** (-i / (dim // 4)) for i in range(dim // 4)], device=dev)
+        us = _time(lambda: o.rotary_cache_write(zq[:, :cols], inv, dim // 2, 1, True, 1e-6, q, kp, vp, pos, seq, slot,
+                                                table, H, G, G, dim, dim, 1, bias=bias, values_are_keys=True), iters)
+        report("rotary_cache_write (v = k, bias)", case, us, n_tok * (cols * 4.0 + (H + 2 * G) * dim * 2.0), 0.0)
+        bias3, wn = torch.zeros(cols + G * dim, device=dev), torch.ones(dim, device=dev)
+        us = _time(lambda: o.qk_norm_cache_write(zq, bias3, wn, wn, 1e-5, q, kp, vp, pos, seq, slot, table, H, G, dim,
+                                                 dim), iters)
+        report("  like: qk_norm_cache_write", case, us, n_tok * (cols + G * dim) * 6.0, 0.0)
+        # --- the delta rule: preparation and walk, beside the closest model's gated linear attention at equal state
+        rh, rg, rd, rv, taps = z["r_heads"], z["r_kv_heads"], z["r_dim"], z["r_vdim"], z["conv"]
+        C = 2 * rg * rd + rh * rv
+        zz = torch.randn((n_tok, C + rh * rv + 2 * rh), device=dev)
+        y = torch.empty((n_tok, C), device=dev)
+        gates = torch.empty((n_tok, 2 * rh + rg), device=dev)
+        kept = torch.zeros((seqs, taps - 1, C), device=dev)
+        tw = torch.randn((C, taps), device=dev)
+        na, dtb = -torch.ones(rh, device=dev), torch.zeros(rh, device=dev)
+        state = torch.zeros((seqs, rh, rd, rv), device=dev)
+        so = torch.empty((n_tok, rh * rv), device=dev)
+
+        def prep():
+            o.delta_prep(zz, tw, kept, y, gates, na, dtb, C + rh * rv, C + rh * rv + rh, seq, start, slot, rg, rh, rd,
+                         rv, 1e-6, rd ** -0.5)
+            o.conv_state_update(zz, kept, start, slot, C)
+        us = _time(prep, iters)
+        report("delta_prep + conv_state_update", case, us, n_tok * (C * 8.0 + (4 * rh + rg) * 4.0) + seqs * (taps - 1) * C * 8.0, 0.0)
+        us = _time(lambda: o.delta_scan(y, gates, state, so, start, slot, rg, rh, rd, rv), few)
+        scan_b = n_tok * (C + 2 * rh + rg + rh * rv) * 4.0 + seqs * rh * rd * rv * 8.0
+        report("delta_scan", case, us, scan_b, 6.0 * n_tok * rh * rd * rv)
+        hd, hv = rh * rd, rh * rv
+        z3 = torch.randn((n_tok, 2 * hd + 2 * hv), device=dev)
+        za = torch.randn((n_tok, hd), device=dev) + 3.0
+        ab = torch.zeros(hd, device=dev)
+        state.zero_()
+        us = _time(lambda: o.gla_scan(z3[:, :hd], z3[:, hd:2 * hd], z3[:, 2 * hd:2 * hd + hv], za, ab, 16.0, 0.125,
+                                      state, so, start, slot, rh, rd, rv, workspace=ws), few)
+        report("  like: gla_scan (third design)", case, us, n_tok * (3 * hd + 2 * hv) * 4.0 + seqs * hd * rv * 8.0,
+               4.0 * n_tok * hd * rv)
+        # --- lightning attention: activation, the scan with constant decays, the norm over all heads
+        lh, ld_, lv = z["l_heads"], z["l_dim"], z["l_vdim"]
+        hd, hv = lh * ld_, lh * lv
+        z4 = torch.randn((n_tok, 2 * hd + 2 * hv), device=dev)
+        us = _time(lambda: o.silu_rows(z4[:, :2 * hd + hv]), iters)
+        report("silu_rows", case, us, n_tok * (2 * hd + hv) * 8.0, 0.0)
+        dec = torch.full((1, hd), 0.97, device=dev)
+        st2 = torch.zeros((seqs, lh, ld_, lv), device=dev)
+        so2 = torch.empty((n_tok, hv), device=dev)
+        us = _time(lambda: o.gla_scan(z4[:, :hd], z4[:, hd:2 * hd], z4[:, 2 * hd:2 * hd + hv], dec, None, 1.0, 1.0,
+                                      st2, so2, start, slot, lh, ld_, lv, workspace=ws, given=True), few)
+        report("gla_scan (constant decays)", case, us, n_tok * (2 * hd + 2 * hv) * 4.0 + seqs * hd * lv * 8.0,
+               4.0 * n_tok * hd * lv)
+        gated = torch.empty((n_tok, hv), device=dev, dtype=bf)
+        nw = torch.ones(hv, device=dev)
+        us = _time(lambda: o.headnorm_silu_gate(so2, nw, 1e-6, z4[:, 2 * hd + hv:], gated, 1, hv, sigmoid=True), iters)
+        report("headnorm gate (one wide head)", case, us, n_tok * hv * 10.0, 0.0)
+        nv = torch.ones(lv, device=dev)
+        us = _time(lambda: o.headnorm_silu_gate(so2, nv, 1e-6, z4[:, 2 * hd + hv:], gated, lh, lv), iters)
+        report("  like: headnorm gate (per head)", case, us, n_tok * hv * 10.0, 0.0)
+        # --- latent attention with a sink beside the same kernel without (second design), and the value
+        # up-projection without a gate beside the gated one
+        mh, rank, rot, mv = z["m_heads"], z["kv_rank"], z["m_rot"], z["m_vdim"]
+        width = rank + rot
+        pages_per = (past + per + 63) // 64
+        ltab = torch.arange(seqs * pages_per, dtype=torch.int32, device=dev).view(seqs, pages_per)
+        pages = torch.randn((seqs * pages_per, 64, width), device=dev, dtype=bf)
+        ql = torch.randn((n_tok, mh * width), device=dev) * 0.1
+        mix = torch.empty((n_tok, mh, rank), device=dev)
+        inv2 = torch.tensor([5e5 ** (-i / (rot // 2)) for i in range(rot // 2)], device=dev)
+        lsink = torch.zeros(mh, device=dev)
+        all_seen = sum(p + 1 for p in range(past, past + per)) * seqs
+        lat_b = 2.0 * seqs * (past + per) * width + n_tok * mh * (width + rank) * 4.0
+        us = _time(lambda: o.latent_attn(ql, width, ql, width, rank, pages, mix, pos, seq, slot, ltab, inv2, mh, rank,
+                                         rot, rot, None, 0.04, max_keys=past + per, workspace=ws, sink=lsink), few)
+        report("latent_attn (sink, no window)", case, us, lat_b, 2.0 * mh * all_seen * (width + rank))
+        us = _time(lambda: o.latent_attn(ql, width, ql, width, rank, pages, mix, pos, seq, slot, ltab, inv2, mh, rank,
+                                         rot, rot, None, 0.04, max_keys=past + per, workspace=ws), few)
+        report("  like: latent_attn (second design)", case, us, lat_b, 2.0 * mh * all_seen * (width + rank))
+        wuv = torch.randn((mh, mv, rank), device=dev, dtype=bf) * 0.02
+        og = torch.empty((n_tok, mh * mv), device=dev, dtype=bf)
+        gl = torch.randn((n_tok, mh * mv), device=dev)
+        us = _time(lambda: o.headwise_gemm(mix.view(n_tok, mh * rank), rank, wuv, og, mv, act_out=True), iters)
+        report("headwise_gemm (values)", case, us, mh * mv * rank * 2.0 + n_tok * mh * (rank * 4.0 + mv * 2.0),
+               2.0 * n_tok * mh * mv * rank)
+        us = _time(lambda: o.headwise_gemm(mix.view(n_tok, mh * rank), rank, wuv, og, mv, gate=gl), iters)
+        report("  like: headwise_gemm (gated)", case, us, mh * mv * rank * 2.0 + n_tok * mh * (rank * 4.0 + mv * 6.0),
+               2.0 * n_tok * mh * mv * rank)
+        # --- the sum of the two mixers, beside the closest model's norm and mean of its two
+        y1, y2, x = (torch.randn((n_tok, W), device=dev) for _ in range(3))
+        ob = torch.zeros(W, device=dev)
+        us = _time(lambda: o.weighted_sum([y1, y2], [ob, None], [1.2, 1.1], x, accumulate=True), iters)
+        report("weighted_sum (two mixers, bias)", case, us, n_tok * W * 16.0, 0.0)
+        w32 = torch.ones(W, device=dev)
+        us = _time(lambda: o.branch_norm_mean([y1, y2], [w32, w32], 1e-5, x, accumulate=True), iters)
+        report("  like: branch_norm_mean", case, us, n_tok * W * 16.0, 0.0)
+    return rows
+
+
 def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     from . import from_random
     from .config import config_from_dict
