@@ -11,7 +11,8 @@
 //   delta_prep          the step's projections -> convolved, activated, unit-normed q, k, v; beta, g and
 //                       k . q per token (everything the walk needs that does not depend on the state)
 //   conv_state_update   the last taps - 1 inputs of every sequence go back to its slot
-//   delta_scan          the walk over each sequence's tokens of the step, in order
+//   delta_scan          the walk over each sequence's tokens of the step, in order (two layouts: one for
+//                       steps of few tokens per sequence, one for many)
 // and three small kernels that the design's other mixers use: silu over the columns of a 32-bit product,
 // a bias added to every row, and the weighted sum of mixers that run side by side.
 //
@@ -237,6 +238,124 @@ delta_scan_kernel(const float* __restrict__ y, int ldy, const float* __restrict_
   }
 }
 
+// The walk for steps of many tokens.  Four lanes share a column of the state, each holding a quarter of its
+// rows (ROWS each; the 16-byte pieces of a row vector go to the four lanes in turn, so that the lanes of a
+// warp read neighbouring pieces of shared memory), so a token's two sums cross two shuffles instead of five
+// and a warp covers eight columns.  A block takes one (sequence, head) and 32 columns; the tokens' q, k and
+// gates come through shared memory in tiles of DR_TILE tokens, the next tile on its way (cp.async) while
+// this one is walked.
+#define DR_TILE 16
+
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int ROWS>
+__global__ void __launch_bounds__(128)
+delta_scan_tiled_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gates,
+                        float* __restrict__ state, float* __restrict__ o, int ldo,
+                        const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int G, int H, int dim,
+                        int vdim) {
+  constexpr int DP = 4 * ROWS;                               // rows, padded
+  __shared__ __align__(16) float kq_s[2][DR_TILE][2 * DP];   // per token: k, then q
+  __shared__ float g_s[2][DR_TILE][4];                       // per token: beta, decay, k . q
+  pdl_wait();
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 3;
+  const int col = (blockIdx.z * 4 + warp) * 8 + (lane >> 2);
+  const bool live = col < vdim;
+  const int g = h / (H / G);
+  const int t0 = seq_start[b], t1 = seq_start[b + 1];
+  const int gw = 2 * H + G;
+  float* S = state + (((size_t)seq_slot[b] * H + h) * dim) * vdim;
+  // register i = 4 j + e holds row 4 (4 j + sub) + e
+  float s[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int row = 4 * (4 * (i >> 2) + sub) + (i & 3);
+    s[i] = (live && row < dim) ? S[(size_t)row * vdim + col] : 0.0f;
+  }
+  // rows past `dim` stay zero in both buffers: they are never copied into
+  for (int idx = threadIdx.x; idx < 2 * DR_TILE * 2 * DP; idx += blockDim.x) (&kq_s[0][0][0])[idx] = 0.0f;
+  __syncthreads();
+  const float* yk = y + (size_t)(G + g) * dim;
+  const float* yq = y + (size_t)g * dim;
+  auto fetch = [&](int buf, int tb) {
+    const int n = min(DR_TILE, t1 - tb);
+    for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
+      const int tt = idx / dim, i = idx - tt * dim;
+      dr_cp4(&kq_s[buf][tt][i], yk + (size_t)(tb + tt) * ldy + i);
+      dr_cp4(&kq_s[buf][tt][DP + i], yq + (size_t)(tb + tt) * ldy + i);
+    }
+    if ((int)threadIdx.x < n) {
+      const float* gr = gates + (size_t)(tb + threadIdx.x) * gw;
+      dr_cp4(&g_s[buf][threadIdx.x][0], gr + h);
+      dr_cp4(&g_s[buf][threadIdx.x][1], gr + H + h);
+      dr_cp4(&g_s[buf][threadIdx.x][2], gr + 2 * H + g);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (t0 < t1) fetch(0, t0);
+  int buf = 0;
+  for (int tb = t0; tb < t1; tb += DR_TILE, buf ^= 1) {
+    const int n = min(DR_TILE, t1 - tb);
+    if (tb + DR_TILE < t1) {
+      fetch(buf ^ 1, tb + DR_TILE);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    float vv[DR_TILE];
+#pragma unroll
+    for (int tt = 0; tt < DR_TILE; ++tt)
+      vv[tt] = (live && tt < n) ? y[(size_t)(tb + tt) * ldy + 2 * G * dim + h * vdim + col] : 0.0f;
+    __syncthreads();
+#pragma unroll
+    for (int tt = 0; tt < DR_TILE; ++tt) {
+      if (tt < n) {
+        const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tt][0]);
+        const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tt][DP]);
+        const float beta = g_s[buf][tt][0], dec = g_s[buf][tt][1], kq = g_s[buf][tt][2];
+        float r[4] = {0.0f, 0.0f, 0.0f, 0.0f}, p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float4 k4[ROWS / 4];
+#pragma unroll
+        for (int j = 0; j < ROWS / 4; ++j) {
+          k4[j] = kk[4 * j + sub];
+          const float4 q4 = qq[4 * j + sub];
+          r[0] = fmaf(s[4 * j], k4[j].x, r[0]);     p[0] = fmaf(s[4 * j], q4.x, p[0]);
+          r[1] = fmaf(s[4 * j + 1], k4[j].y, r[1]); p[1] = fmaf(s[4 * j + 1], q4.y, p[1]);
+          r[2] = fmaf(s[4 * j + 2], k4[j].z, r[2]); p[2] = fmaf(s[4 * j + 2], q4.z, p[2]);
+          r[3] = fmaf(s[4 * j + 3], k4[j].w, r[3]); p[3] = fmaf(s[4 * j + 3], q4.w, p[3]);
+        }
+        float rs = (r[0] + r[1]) + (r[2] + r[3]), ps = (p[0] + p[1]) + (p[2] + p[3]);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        // the sums were taken over the state before its decay: s' = dec s
+        const float u = beta * (vv[tt] - dec * rs);
+        if (live && sub == 0) o[(size_t)(tb + tt) * ldo + h * vdim + col] = fmaf(u, kq, dec * ps);
+#pragma unroll
+        for (int j = 0; j < ROWS / 4; ++j) {
+          s[4 * j] = fmaf(k4[j].x, u, dec * s[4 * j]);
+          s[4 * j + 1] = fmaf(k4[j].y, u, dec * s[4 * j + 1]);
+          s[4 * j + 2] = fmaf(k4[j].z, u, dec * s[4 * j + 2]);
+          s[4 * j + 3] = fmaf(k4[j].w, u, dec * s[4 * j + 3]);
+        }
+      }
+    }
+    __syncthreads();      // the next round's copies overwrite the buffer that was just read
+  }
+  pdl_launch_dependents();
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int row = 4 * (4 * (i >> 2) + sub) + (i & 3);
+    if (live && row < dim) S[(size_t)row * vdim + col] = s[i];
+  }
+}
+
 extern "C" int TL_NAME(tl_delta_prep)(const float* z, int ld, const float* taps_w, int taps, const float* kept,
                                       float* y, int ldy, float* gates, const float* neg_a, const float* dt_bias,
                                       int col_b, int col_a, const int* token_seq, const int* seq_start,
@@ -263,12 +382,24 @@ extern "C" int TL_NAME(tl_conv_state_update)(const float* z, int ld, float* kept
 }
 
 extern "C" int TL_NAME(tl_delta_scan)(const float* y, int ldy, const float* gates, float* state, float* o, int ldo,
-                                      const int* seq_start, const int* seq_slot, int B, int G, int H, int dim,
-                                      int vdim, cudaStream_t stream) {
+                                      const int* seq_start, const int* seq_slot, int T, int B, int G, int H,
+                                      int dim, int vdim, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (G < 1 || H < 1 || H % G || dim < 1 || vdim < 1) return TL_ERR_BAD_ARG;
   const int R = (dim + 31) / 32;
   if (H > 65535 || R > DR_MAX_R) return TL_ERR_UNSUPPORTED;
+  if (T >= 8 * B && dim <= 128) {
+    // many tokens per sequence: four lanes a column, operands through shared memory
+    dim3 tg(B, H, (vdim + 31) / 32);
+    if (tg.z > 65535) return TL_ERR_UNSUPPORTED;
+#define TILED(ROWS_)                                                                                          \
+    return tl_launch(delta_scan_tiled_kernel<ROWS_>, tg, dim3(128), 0, stream, y, ldy, gates, state, o, ldo,  \
+                     seq_start, seq_slot, G, H, dim, vdim)
+    if (dim <= 32) TILED(8);
+    if (dim <= 64) TILED(16);
+    TILED(32);
+#undef TILED
+  }
   const int per_block = DR_WARPS * DR_COLS;
   dim3 grid(B, H, (vdim + per_block - 1) / per_block);
   if (grid.z > 65535) return TL_ERR_UNSUPPORTED;

@@ -354,6 +354,30 @@ headnorm_silu_gate_kernel(const float* __restrict__ o, const float* __restrict__
   }
 }
 
+// The same for heads too wide for a warp (a norm over the concatenated heads of a whole row): a block per
+// (t, h), the sum of squares over the block, the row read a second time from cache.
+__global__ void __launch_bounds__(256)
+headnorm_gate_wide_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                          const float* __restrict__ g, int ldg, act_t* __restrict__ out, int heads, int vdim,
+                          int gate_act) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int t = r / heads, h = r - t * heads;
+  const float* src = o + (size_t)r * vdim;
+  const float* gate = g + (size_t)t * ldg + (size_t)h * vdim;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < vdim; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+  for (int i = threadIdx.x; i < vdim; i += blockDim.x) {
+    const float z = gate[i];
+    const float sg = 1.0f / (1.0f + expf(-z));
+    out[(size_t)r * vdim + i] = from_f32<act_t>(src[i] * inv * w[i] * (gate_act == 0 ? z * sg : sg));
+  }
+}
+
 extern "C" int TL_NAME(tl_headnorm_silu_gate)(const float* o, const float* w, float eps, const float* g, int ldg,
                                               void* out, int T, int heads, int vdim, int gate_act,
                                               cudaStream_t stream) {
@@ -361,6 +385,9 @@ extern "C" int TL_NAME(tl_headnorm_silu_gate)(const float* o, const float* w, fl
   if (heads < 1 || vdim < 1) return TL_ERR_BAD_ARG;
   const long long rows = (long long)T * heads;
   if (rows > 0x7fffffffLL) return TL_ERR_UNSUPPORTED;
+  if (vdim > 512)
+    return tl_launch(headnorm_gate_wide_kernel, dim3((unsigned)rows), dim3(256), 0, stream, o, w, eps, g, ldg,
+                     (act_t*)out, heads, vdim, gate_act);
   const unsigned blocks = (unsigned)((rows + 7) / 8);
   return tl_launch(headnorm_silu_gate_kernel, dim3(blocks), dim3(256), 0, stream, o, w, eps, g, ldg, (act_t*)out,
                    (int)rows, heads, vdim, gate_act);

@@ -753,8 +753,9 @@ class CoreOps:
                 out.shape != (T, heads * vdim) or state.shape[1:] != (heads, dim, vdim):
             raise KernelError("delta_scan: sizes do not match")
         _check(self._tl_delta_scan(_ptr(y), c_int(y.stride(0)), _ptr(gates), _ptr(state), _ptr(out),
-                                   c_int(out.stride(0)), _ptr(seq_start), _ptr(seq_slot), c_int(seq_slot.numel()),
-                                   c_int(kv_heads), c_int(heads), c_int(dim), c_int(vdim), _stream()), "delta_scan")
+                                   c_int(out.stride(0)), _ptr(seq_start), _ptr(seq_slot), c_int(T),
+                                   c_int(seq_slot.numel()), c_int(kv_heads), c_int(heads), c_int(dim), c_int(vdim),
+                                   _stream()), "delta_scan")
 
     def silu_rows(self, x: torch.Tensor) -> None:
         """x <- silu(x) in place; x 32-bit [T, n], rows may be strided."""
