@@ -356,7 +356,7 @@ headnorm_silu_gate_kernel(const float* __restrict__ o, const float* __restrict__
 
 // The same for heads too wide for a warp (a norm over the concatenated heads of a whole row): a block per
 // (t, h), the sum of squares over the block, the row read a second time from cache.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 headnorm_gate_wide_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
                           const float* __restrict__ g, int ldg, act_t* __restrict__ out, int heads, int vdim,
                           int gate_act) {
@@ -368,6 +368,7 @@ headnorm_gate_wide_kernel(const float* __restrict__ o, const float* __restrict__
   const float* src = o + (size_t)r * vdim;
   const float* gate = g + (size_t)t * ldg + (size_t)h * vdim;
   float ss = 0.0f;
+#pragma unroll 4
   for (int i = threadIdx.x; i < vdim; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
@@ -386,7 +387,7 @@ extern "C" int TL_NAME(tl_headnorm_silu_gate)(const float* o, const float* w, fl
   const long long rows = (long long)T * heads;
   if (rows > 0x7fffffffLL) return TL_ERR_UNSUPPORTED;
   if (vdim > 512)
-    return tl_launch(headnorm_gate_wide_kernel, dim3((unsigned)rows), dim3(256), 0, stream, o, w, eps, g, ldg,
+    return tl_launch(headnorm_gate_wide_kernel, dim3((unsigned)rows), dim3(vdim >= 2048 ? 1024 : 256), 0, stream, o, w, eps, g, ldg,
                      (act_t*)out, heads, vdim, gate_act);
   const unsigned blocks = (unsigned)((rows + 7) / 8);
   return tl_launch(headnorm_silu_gate_kernel, dim3(blocks), dim3(256), 0, stream, o, w, eps, g, ldg, (act_t*)out,
