@@ -131,18 +131,18 @@ def test_a_branch_that_asks_for_two_things_inside_a_mixer_that_asks_for_two():
 def test_frequencies_stretched_band_by_band():
     """The three bands: short waves keep their frequency, long ones are slowed by the factor, between them the two
     are blended with a weight that runs from 0 to 1; the package's table and the plain one agree."""
-    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 512}}
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 6.0, "low": 1.0, "high": 4.0, "original": 1024}}
     f0 = plain.frequencies({"base": 10000.0, "dims": 64})
     f = plain.frequencies(rot)
     wave = 2 * math.pi / f0
     assert np.allclose(f0, 10000.0 ** (-np.arange(32) / 32.0))
-    short, long_ = wave < 512 / 4.0, wave > 512 / 1.0
+    short, long_ = wave < 1024 / 4.0, wave > 1024 / 1.0
     assert short.any() and long_.any() and (~short & ~long_).any()
-    assert np.array_equal(f[short], f0[short]) and np.allclose(f[long_], f0[long_] / 8.0)
+    assert np.array_equal(f[short], f0[short]) and np.allclose(f[long_], f0[long_] / 6.0)
     mid = ~short & ~long_
-    assert np.all(f[mid] < f0[mid]) and np.all(f[mid] > f0[mid] / 8.0)
-    s = (512 / wave[mid] - 1.0) / 3.0
-    assert np.allclose(f[mid], (1 - s) * f0[mid] / 8.0 + s * f0[mid])
+    assert np.all(f[mid] < f0[mid]) and np.all(f[mid] > f0[mid] / 6.0)
+    s = (1024 / wave[mid] - 1.0) / 3.0
+    assert np.allclose(f[mid], (1 - s) * f0[mid] / 6.0 + s * f0[mid])
     table = RotaryHalfSplit.frequencies(64, 10000.0, rot["scaling"]).numpy()
     assert np.allclose(table, f, rtol=1e-14)
     assert np.allclose(RotaryHalfSplit.frequencies(64, 10000.0).numpy(), f0, rtol=1e-14)
