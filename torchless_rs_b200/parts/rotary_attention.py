@@ -49,6 +49,7 @@ class _RotaryAttention:
     can_overwrite = True
     slots = 1            # query/key maps per head
     unit_norm = False    # q and k divided by their root mean square after the rotation
+    plain_scores = True  # nothing but the keys enters the softmax (False: a sink does; the plain kernels are not built)
     proj_bias = None     # 32-bit, one number per column of the stacked projections (None: no bias)
     values_are_keys = False   # no value projection: a head's values are its keys as projected
 
@@ -76,7 +77,7 @@ class _RotaryAttention:
         # scores without a cap over keys and values of one size are what the framework's plain
         # attention kernels compute (tensor-memory kernels for prompts, split keys for decode steps)
         self.fast = None
-        if not rt.is_f32 and self.width == self.vdim:
+        if not rt.is_f32 and self.width == self.vdim and self.plain_scores:
             from ..csrc import attention_bf16
             if self.width in attention_bf16.FAST_HEAD_DIMS:
                 self.fast = attention_bf16.AttentionBf16.get(self.width)
@@ -225,6 +226,7 @@ class SinkRotaryAttention(_RotaryAttention):
         p = spec.params
         self.unit_norm = bool(p.get("unit_norm", False))
         self.values_are_keys = bool(p.get("values_are_keys", False))
+        self.plain_scores = not bool(p.get("sink", False))
         super().__init__(spec, prefix, rt, position)
         self.window = int(p["window"]) if p.get("window") else None
         self.has_sink = bool(p.get("sink", False))
