@@ -355,7 +355,8 @@ headnorm_silu_gate_kernel(const float* __restrict__ o, const float* __restrict__
 }
 
 // The same for heads too wide for a warp (a norm over the concatenated heads of a whole row): a block per
-// (t, h), the sum of squares over the block, the row read a second time from cache.
+// (t, h), the sum of squares over the block, the row read a second time from cache.  Few rows (decode
+// steps) get blocks of 1024 threads, so that a thread's loads are few and in flight together.
 __global__ void __launch_bounds__(1024)
 headnorm_gate_wide_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
                           const float* __restrict__ g, int ldg, act_t* __restrict__ out, int heads, int vdim,
@@ -387,7 +388,7 @@ extern "C" int TL_NAME(tl_headnorm_silu_gate)(const float* o, const float* w, fl
   const long long rows = (long long)T * heads;
   if (rows > 0x7fffffffLL) return TL_ERR_UNSUPPORTED;
   if (vdim > 512)
-    return tl_launch(headnorm_gate_wide_kernel, dim3((unsigned)rows), dim3(vdim >= 2048 ? 1024 : 256), 0, stream, o, w, eps, g, ldg,
+    return tl_launch(headnorm_gate_wide_kernel, dim3((unsigned)rows), dim3(vdim >= 2048 && rows < 512 ? 1024 : 256), 0, stream, o, w, eps, g, ldg,
                      (act_t*)out, heads, vdim, gate_act);
   const unsigned blocks = (unsigned)((rows + 7) / 8);
   return tl_launch(headnorm_silu_gate_kernel, dim3(blocks), dim3(256), 0, stream, o, w, eps, g, ldg, (act_t*)out,
