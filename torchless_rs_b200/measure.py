@@ -1078,14 +1078,14 @@ def timeline(B: int, context: int, layers: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline", "decode",
-                                     "kikopel-kernels", "tovapel-kernels", "rupasun-kernels"])
+                                     "kikopel-kernels", "tovapel-kernels", "rupasun-kernels", "fezolorn-kernels"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     ap.add_argument("--model", default="mistral7b", choices=sorted(MODEL_SIZES),
                     help="step, timeline: whose layer sizes the model has")
     ap.add_argument("--kikopel-size", default="1b", choices=sorted(KIKOPEL_SIZES),
-                    help="kikopel-kernels / tovapel-kernels / rupasun-kernels TOKENS BATCH CONTEXT: whose layer sizes "
+                    help="kikopel-kernels / tovapel-kernels / rupasun-kernels / fezolorn-kernels TOKENS BATCH CONTEXT: whose layer sizes "
                          "the kernels get")
     ap.add_argument("--window", type=int, default=0, help="decode: the sliding window (0: none)")
     ap.add_argument("--equal-shares", action="store_true",
@@ -1103,6 +1103,9 @@ def main() -> None:
         return
     if a.what == "rupasun-kernels":
         rupasun_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
+        return
+    if a.what == "fezolorn-kernels":
+        fezolorn_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
         return
     if a.what == "kikopel-kernels":
         kikopel_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
