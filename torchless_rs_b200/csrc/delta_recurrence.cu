@@ -238,12 +238,13 @@ delta_scan_kernel(const float* __restrict__ y, int ldy, const float* __restrict_
   }
 }
 
-// The walk for steps of many tokens.  Four lanes share a column of the state, each holding a quarter of its
-// rows (ROWS each; the 16-byte pieces of a row vector go to the four lanes in turn, so that the lanes of a
-// warp read neighbouring pieces of shared memory), so a token's two sums cross two shuffles instead of five
-// and a warp covers eight columns.  A block takes one (sequence, head) and 32 columns; the tokens' q, k and
-// gates come through shared memory in tiles of DR_TILE tokens, the next tile on its way (cp.async) while
-// this one is walked.
+// The walk for steps of many tokens.  LPC lanes share a column of the state, each holding ROWS of its rows
+// (the 16-byte pieces of a row vector go to the lanes in turn, so that the lanes of a warp read neighbouring
+// pieces of shared memory); a warp covers 32 / LPC columns, a block one (sequence, head) and four warps'
+// columns.  The tokens' q, k and gates come through shared memory in tiles of DR_TILE tokens, the next tile
+// on its way (cp.async) while this one is walked.  A walk has sequences x heads x columns chains that wait
+// for nothing but themselves and the GPU has room for more warps than that, so a column is spread over as
+// many lanes as leave each lane a piece or two: what a warp executes per token is what the step takes.
 #define DR_TILE 16
 
 __device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
@@ -251,30 +252,41 @@ __device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int ROWS>
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void dr_store_if(float* p, float v, bool yes) {
+  asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q st.global.f32 [%0], %1;\n}" ::"l"(p), "f"(v), "r"((int)yes)
+               : "memory");
+}
+
+template <int ROWS, int LPC>
 __global__ void __launch_bounds__(128)
 delta_scan_tiled_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gates,
                         float* __restrict__ state, float* __restrict__ o, int ldo,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int G, int H, int dim,
                         int vdim) {
-  constexpr int DP = 4 * ROWS;                               // rows, padded
+  constexpr int DP = LPC * ROWS;                             // rows, padded
+  constexpr int CPW = 32 / LPC;                              // columns of a warp
   __shared__ __align__(16) float kq_s[2][DR_TILE][2 * DP];   // per token: k, then q
-  __shared__ float g_s[2][DR_TILE][4];                       // per token: beta, decay, k . q
+  __shared__ __align__(16) float g_s[2][DR_TILE][4];         // per token: beta, decay, k . q
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane & 3;
-  const int col = (blockIdx.z * 4 + warp) * 8 + (lane >> 2);
+  const int sub = lane & (LPC - 1);
+  const int col = (blockIdx.z * 4 + warp) * CPW + lane / LPC;
   const bool live = col < vdim;
   const int g = h / (H / G);
   const int t0 = seq_start[b], t1 = seq_start[b + 1];
   const int gw = 2 * H + G;
   float* S = state + (((size_t)seq_slot[b] * H + h) * dim) * vdim;
-  // register i = 4 j + e holds row 4 (4 j + sub) + e
+  // register i = 4 j + e holds row 4 (LPC j + sub) + e
   float s[ROWS];
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int row = 4 * (4 * (i >> 2) + sub) + (i & 3);
+    const int row = 4 * (LPC * (i >> 2) + sub) + (i & 3);
     s[i] = (live && row < dim) ? S[(size_t)row * vdim + col] : 0.0f;
   }
   // rows past `dim` stay zero in both buffers: they are never copied into
@@ -282,18 +294,37 @@ delta_scan_tiled_kernel(const float* __restrict__ y, int ldy, const float* __res
   __syncthreads();
   const float* yk = y + (size_t)(G + g) * dim;
   const float* yq = y + (size_t)g * dim;
+  // eight threads copy one token's k and q, in 16-byte pieces where the rows allow it
+  const bool wide = (dim & 3) == 0 && (ldy & 3) == 0 && ((uintptr_t)y & 15) == 0;
+  const int ft = threadIdx.x >> 3, fp = threadIdx.x & 7;
   auto fetch = [&](int buf, int tb) {
     const int n = min(DR_TILE, t1 - tb);
-    for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
-      const int tt = idx / dim, i = idx - tt * dim;
-      dr_cp4(&kq_s[buf][tt][i], yk + (size_t)(tb + tt) * ldy + i);
-      dr_cp4(&kq_s[buf][tt][DP + i], yq + (size_t)(tb + tt) * ldy + i);
+    if (ft < n) {
+      const float* rk = yk + (size_t)(tb + ft) * ldy;
+      const float* rq = yq + (size_t)(tb + ft) * ldy;
+      if (wide) {
+        for (int i = fp * 4; i < dim; i += 32) {
+          dr_cp16(&kq_s[buf][ft][i], rk + i);
+          dr_cp16(&kq_s[buf][ft][DP + i], rq + i);
+        }
+      } else {
+        for (int i = fp; i < dim; i += 8) {
+          dr_cp4(&kq_s[buf][ft][i], rk + i);
+          dr_cp4(&kq_s[buf][ft][DP + i], rq + i);
+        }
+      }
     }
     if ((int)threadIdx.x < n) {
       const float* gr = gates + (size_t)(tb + threadIdx.x) * gw;
       dr_cp4(&g_s[buf][threadIdx.x][0], gr + h);
       dr_cp4(&g_s[buf][threadIdx.x][1], gr + H + h);
       dr_cp4(&g_s[buf][threadIdx.x][2], gr + 2 * H + g);
+    } else if ((int)threadIdx.x < DR_TILE) {
+      // a place past the step's end writes nothing (beta 0) and decays nothing, so the walk below needs no
+      // branch per token and its loads can run ahead of the token before
+      g_s[buf][threadIdx.x][0] = 0.0f;
+      g_s[buf][threadIdx.x][1] = 1.0f;
+      g_s[buf][threadIdx.x][2] = 0.0f;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -311,39 +342,68 @@ delta_scan_tiled_kernel(const float* __restrict__ y, int ldy, const float* __res
 #pragma unroll
     for (int tt = 0; tt < DR_TILE; ++tt)
       vv[tt] = (live && tt < n) ? y[(size_t)(tb + tt) * ldy + 2 * G * dim + h * vdim + col] : 0.0f;
+    float* o_col = o + (size_t)tb * ldo + h * vdim + (live ? col : 0);
+    const bool writes = live && sub == 0;
     __syncthreads();
+    // a token's k, q and gates are asked for while the token before is worked on
+    float4 k4[ROWS / 4], q4[ROWS / 4], gt;
+    {
+      const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][0][0]);
+      const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][0][DP]);
+#pragma unroll
+      for (int j = 0; j < ROWS / 4; ++j) {
+        k4[j] = kk[LPC * j + sub];
+        q4[j] = qq[LPC * j + sub];
+      }
+      gt = *reinterpret_cast<const float4*>(&g_s[buf][0][0]);
+    }
 #pragma unroll
     for (int tt = 0; tt < DR_TILE; ++tt) {
-      if (tt < n) {
-        const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tt][0]);
-        const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tt][DP]);
-        const float beta = g_s[buf][tt][0], dec = g_s[buf][tt][1], kq = g_s[buf][tt][2];
-        float r[4] = {0.0f, 0.0f, 0.0f, 0.0f}, p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        float4 k4[ROWS / 4];
+      float4 k4n[ROWS / 4], q4n[ROWS / 4], gtn;
+      if (tt + 1 < DR_TILE) {
+        const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tt + 1][0]);
+        const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tt + 1][DP]);
 #pragma unroll
         for (int j = 0; j < ROWS / 4; ++j) {
-          k4[j] = kk[4 * j + sub];
-          const float4 q4 = qq[4 * j + sub];
-          r[0] = fmaf(s[4 * j], k4[j].x, r[0]);     p[0] = fmaf(s[4 * j], q4.x, p[0]);
-          r[1] = fmaf(s[4 * j + 1], k4[j].y, r[1]); p[1] = fmaf(s[4 * j + 1], q4.y, p[1]);
-          r[2] = fmaf(s[4 * j + 2], k4[j].z, r[2]); p[2] = fmaf(s[4 * j + 2], q4.z, p[2]);
-          r[3] = fmaf(s[4 * j + 3], k4[j].w, r[3]); p[3] = fmaf(s[4 * j + 3], q4.w, p[3]);
+          k4n[j] = kk[LPC * j + sub];
+          q4n[j] = qq[LPC * j + sub];
         }
-        float rs = (r[0] + r[1]) + (r[2] + r[3]), ps = (p[0] + p[1]) + (p[2] + p[3]);
-        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-        // the sums were taken over the state before its decay: s' = dec s
-        const float u = beta * (vv[tt] - dec * rs);
-        if (live && sub == 0) o[(size_t)(tb + tt) * ldo + h * vdim + col] = fmaf(u, kq, dec * ps);
+        gtn = *reinterpret_cast<const float4*>(&g_s[buf][tt + 1][0]);
+      }
+      const float beta = gt.x, dec = gt.y, kq = gt.z;
+      float r[4] = {0.0f, 0.0f, 0.0f, 0.0f}, p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int j = 0; j < ROWS / 4; ++j) {
+        r[0] = fmaf(s[4 * j], k4[j].x, r[0]);     p[0] = fmaf(s[4 * j], q4[j].x, p[0]);
+        r[1] = fmaf(s[4 * j + 1], k4[j].y, r[1]); p[1] = fmaf(s[4 * j + 1], q4[j].y, p[1]);
+        r[2] = fmaf(s[4 * j + 2], k4[j].z, r[2]); p[2] = fmaf(s[4 * j + 2], q4[j].z, p[2]);
+        r[3] = fmaf(s[4 * j + 3], k4[j].w, r[3]); p[3] = fmaf(s[4 * j + 3], q4[j].w, p[3]);
+      }
+      float rs = (r[0] + r[1]) + (r[2] + r[3]), ps = (p[0] + p[1]) + (p[2] + p[3]);
+#pragma unroll
+      for (int m = 1; m < LPC; m <<= 1) {
+        rs += __shfl_xor_sync(0xffffffffu, rs, m);
+        ps += __shfl_xor_sync(0xffffffffu, ps, m);
+      }
+      // the sums were taken over the state before its decay: s' = dec s
+      const float u = beta * (vv[tt] - dec * rs);
+      // (a store under a predicate, not a branch: the tile stays one straight run of instructions, so the
+      // loads of later tokens are scheduled ahead of the tokens before)
+      dr_store_if(o_col + (size_t)tt * ldo, fmaf(u, kq, dec * ps), writes && tt < n);
+#pragma unroll
+      for (int j = 0; j < ROWS / 4; ++j) {
+        s[4 * j] = fmaf(k4[j].x, u, dec * s[4 * j]);
+        s[4 * j + 1] = fmaf(k4[j].y, u, dec * s[4 * j + 1]);
+        s[4 * j + 2] = fmaf(k4[j].z, u, dec * s[4 * j + 2]);
+        s[4 * j + 3] = fmaf(k4[j].w, u, dec * s[4 * j + 3]);
+      }
+      if (tt + 1 < DR_TILE) {
 #pragma unroll
         for (int j = 0; j < ROWS / 4; ++j) {
-          s[4 * j] = fmaf(k4[j].x, u, dec * s[4 * j]);
-          s[4 * j + 1] = fmaf(k4[j].y, u, dec * s[4 * j + 1]);
-          s[4 * j + 2] = fmaf(k4[j].z, u, dec * s[4 * j + 2]);
-          s[4 * j + 3] = fmaf(k4[j].w, u, dec * s[4 * j + 3]);
+          k4[j] = k4n[j];
+          q4[j] = q4n[j];
         }
+        gt = gtn;
       }
     }
     __syncthreads();      // the next round's copies overwrite the buffer that was just read
@@ -351,7 +411,7 @@ delta_scan_tiled_kernel(const float* __restrict__ y, int ldy, const float* __res
   pdl_launch_dependents();
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int row = 4 * (4 * (i >> 2) + sub) + (i & 3);
+    const int row = 4 * (LPC * (i >> 2) + sub) + (i & 3);
     if (live && row < dim) S[(size_t)row * vdim + col] = s[i];
   }
 }
@@ -389,15 +449,18 @@ extern "C" int TL_NAME(tl_delta_scan)(const float* y, int ldy, const float* gate
   const int R = (dim + 31) / 32;
   if (H > 65535 || R > DR_MAX_R) return TL_ERR_UNSUPPORTED;
   if (T >= 8 * B && dim <= 128) {
-    // many tokens per sequence: four lanes a column, operands through shared memory
-    dim3 tg(B, H, (vdim + 31) / 32);
+    // many tokens per sequence: several lanes a column, operands through shared memory
+    const int lpc = dim <= 16 ? 4 : (dim <= 32 ? 8 : 16);
+    const int cols = 4 * (32 / lpc);
+    dim3 tg(B, H, (vdim + cols - 1) / cols);
     if (tg.z > 65535) return TL_ERR_UNSUPPORTED;
-#define TILED(ROWS_)                                                                                          \
-    return tl_launch(delta_scan_tiled_kernel<ROWS_>, tg, dim3(128), 0, stream, y, ldy, gates, state, o, ldo,  \
-                     seq_start, seq_slot, G, H, dim, vdim)
-    if (dim <= 32) TILED(8);
-    if (dim <= 64) TILED(16);
-    TILED(32);
+#define TILED(ROWS_, LPC_)                                                                                    \
+    return tl_launch(delta_scan_tiled_kernel<ROWS_, LPC_>, tg, dim3(128), 0, stream, y, ldy, gates, state, o, \
+                     ldo, seq_start, seq_slot, G, H, dim, vdim)
+    if (dim <= 16) TILED(4, 4);
+    if (dim <= 32) TILED(4, 8);
+    if (dim <= 64) TILED(4, 16);
+    TILED(8, 16);
 #undef TILED
   }
   const int per_block = DR_WARPS * DR_COLS;
