@@ -13,8 +13,8 @@
 //   conv_state_update   the last taps - 1 inputs of every sequence go back to its slot
 //   delta_scan          the walk over each sequence's tokens of the step, in order (two layouts: one for
 //                       steps of few tokens per sequence, one for many)
-// and three small kernels that the design's other mixers use: silu over the columns of a 32-bit product,
-// a bias added to every row, and the weighted sum of mixers that run side by side.
+// and two small kernels that the design's other mixers use: silu over the columns of a 32-bit product, and
+// the weighted sum of mixers that run side by side (each with the bias of its output projection, if any).
 //
 // The columns of S are independent of one another (column c only needs v_c and the shared q, k, g,
 // beta), so the walk is spread over (sequence, head, group of columns); a warp owns DR_COLS columns, its
